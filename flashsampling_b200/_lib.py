@@ -1,0 +1,105 @@
+"""ctypes binding of ``lib/libfmms_b200.so`` (the C ABI declared in include/fmms_b200.h).
+
+Loading fails loudly when the shared object is absent: there is no CPU or
+PyTorch fallback for the sampling path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfmms_b200.so"
+
+# status codes / flags (include/fmms_b200.h)
+OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH = range(7)
+FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA = 1, 2, 4, 8, 16
+PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
+
+# every symbol the header declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "fmms_version": (c_int, []),
+    "fmms_strerror": (c_char_p, [c_int]),
+    "fmms_num_sms": (c_int, [ctypes.POINTER(c_int)]),
+    "fmms_query_workspace": (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(c_size_t)]),
+    "fmms_sample": (
+        c_int,
+        [
+            c_void_p,  # W
+            c_void_p,  # H
+            c_void_p,  # temperature
+            c_int,  # temp_stride
+            c_int,  # V_local
+            c_int,  # D
+            c_int,  # B
+            c_int,  # S
+            c_ulonglong,  # seed
+            c_longlong,  # v_global_offset
+            c_int,  # flags
+            c_void_p,  # ext_noise
+            c_longlong,  # noise_ld
+            c_void_p,  # logits_out
+            c_void_p,  # out_idx
+            c_void_p,  # out_val
+            c_void_p,  # workspace
+            c_size_t,  # workspace_bytes
+            c_void_p,  # status_dev
+            c_void_p,  # stream
+        ],
+    ),
+    "fmms_last_path": (c_int, []),
+    "fmms_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
+}
+
+_lib = None
+
+
+class FmmsError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: {strerror(status)} (status {status})")
+
+
+def load() -> ctypes.CDLL:
+    """Load the CUDA library (once) and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flashsampling_b200.build` "
+            "(there is no fallback implementation)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def strerror(status: int) -> str:
+    return load().fmms_strerror(int(status)).decode()
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise FmmsError(status, where)
+
+
+def query_workspace(v_local: int, d: int, b: int, s: int) -> int:
+    n = c_size_t(0)
+    check(load().fmms_query_workspace(v_local, d, b, s, ctypes.byref(n)), "fmms_query_workspace")
+    return int(n.value)
+
+
+PLAN_FIELDS = ("path", "grid", "tile_rows", "tiles_total", "stages", "m_tiles", "smem_bytes", "candidate_rows")
+
+
+def plan(v_local: int, d: int, b: int, s: int, flags: int = 0, num_sms: int = 148, max_smem: int = 232448) -> dict:
+    """Host-side launch plan (no GPU needed); see fmms_plan in the header."""
+    arr = (c_int * 8)()
+    check(load().fmms_plan(v_local, d, b, s, flags, num_sms, max_smem, arr), "fmms_plan")
+    return dict(zip(PLAN_FIELDS, list(arr)))

@@ -1,0 +1,248 @@
+"""Fused LM-head sampling on B200: the Python entry point.
+
+Drop-in for the reference's ``fused_mm_sample_triton`` (src/fused_mm_sampling/
+core.py:224-348) and its provider registry ``get_sampler`` (core.py:658-801):
+same argument names and meaning, same return value (int64 ``[B, num_samples]``
+on the inputs' device, identical on every tensor-parallel rank), errors as
+Python exceptions.  The work is done by hand-written sm_100a CUDA behind the C
+ABI in ``include/fmms_b200.h``; this module only validates, caches scratch
+buffers and forwards raw pointers.  There is no Triton, no other backend and
+no CPU path: without the CUDA library or a GPU the call raises.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Protocol
+
+import torch
+
+from . import _lib
+from .tp_info import TP1, TPInfo
+
+__all__ = [
+    "fused_mm_sample",
+    "fused_mm_sample_triton",
+    "get_sampler",
+    "Sampler",
+    "SimpleSampler",
+    "check_status",
+    "last_path",
+    "PROVIDERS",
+]
+
+_workspaces: dict[tuple, torch.Tensor] = {}
+_status: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream_id)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    st = _status.get(device.index)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device.index] = st
+    return st
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if a kernel recorded a device-side time-out.
+
+    The sampling call itself never synchronises; call this where a sync is
+    acceptable (tests, benchmarks, shutdown).
+    """
+    devs = [device.index] if device is not None else list(_status)
+    for idx in devs:
+        st = _status.get(idx)
+        if st is None:
+            continue
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            raise _lib.FmmsError(code, "fused_mm_sample (device status word)")
+
+
+def last_path() -> str:
+    """Kernel the most recent call dispatched to: "gemv", "mma" or "none"."""
+    return {0: "none", 1: "gemv", 2: "mma"}[_lib.load().fmms_last_path()]
+
+
+def fused_mm_sample(
+    weights: torch.Tensor,  # [V_local, D] bf16 (may be a vocabulary shard)
+    hidden_states: torch.Tensor,  # [B, D] bf16
+    num_samples: int,
+    temperature: torch.Tensor,  # 0-d fp32 tensor on the device, or [B] for per-row temperatures
+    seed: int,
+    greedy_sampling: bool = False,
+    tp: TPInfo = TP1,
+    return_logits: bool = False,
+    p2p_no_overlap: bool = False,
+    noise: torch.Tensor | None = None,  # [num_samples, B, V_local] or [B, V_local] fp32: replaces the generator
+    kernel: str | None = None,  # None = automatic, "gemv" or "mma" forces a kernel
+    return_values: bool = False,
+):
+    """Sample ``num_samples`` token ids per hidden-state row from softmax(W h / T).
+
+    Arguments follow core.py:224-234.  Extensions: ``temperature`` may hold one
+    value per row; ``noise`` supplies the Gumbel noise (parity checks);
+    ``kernel`` pins the kernel; ``return_values`` also returns the winning
+    perturbed logits ``[B, num_samples]``.  ``p2p_no_overlap`` selects the
+    reference's ablation in which the exchange follows the kernel; here the
+    exchange always follows the local reduction, so the flag changes nothing.
+
+    With ``tp.size > 1`` every rank passes its own contiguous vocabulary block
+    and the same ``hidden_states``, ``temperature`` and ``seed``; all ranks
+    return the same global token ids, equal to the single-GPU result.
+    """
+    if not (weights.is_cuda and hidden_states.is_cuda):
+        raise RuntimeError("fused_mm_sample requires CUDA tensors (there is no CPU path)")
+    if weights.ndim != 2 or hidden_states.ndim != 2:
+        raise ValueError("weights must be [V, D] and hidden_states [B, D]")
+    V, D = weights.shape
+    B, D2 = hidden_states.shape
+    if D2 != D:
+        raise ValueError(
+            f"hidden_states second dimension ({D2}) must match weights second dimension ({D})"
+        )
+    if weights.dtype != torch.bfloat16 or hidden_states.dtype != torch.bfloat16:
+        raise TypeError("weights and hidden_states must be bfloat16")
+    if not weights.is_contiguous():
+        raise ValueError("weights must be contiguous")
+    if num_samples < 1:
+        raise ValueError("num_samples must be >= 1")
+    hidden_states = hidden_states.contiguous()
+    dev = weights.device
+    lib = _lib.load()
+
+    flags = 0
+    temp_ptr, temp_stride = None, 0
+    if greedy_sampling:
+        flags |= _lib.FLAG_GREEDY
+    else:
+        if not isinstance(temperature, torch.Tensor):
+            temperature = torch.tensor(float(temperature), dtype=torch.float32, device=dev)
+        if temperature.device != dev or temperature.dtype != torch.float32:
+            temperature = temperature.to(device=dev, dtype=torch.float32)
+        if temperature.numel() == 1:
+            temp_stride = 0
+        elif temperature.numel() == B:
+            temperature = temperature.reshape(B).contiguous()
+            temp_stride = 1
+        else:
+            raise ValueError(f"temperature must have 1 or {B} elements, got {temperature.numel()}")
+        temp_ptr = temperature.data_ptr()
+
+    noise_ptr, noise_ld = None, 0
+    if noise is not None and not greedy_sampling:
+        if noise.ndim == 2:
+            noise = noise[None]
+        if noise.shape != (num_samples, B, V) or noise.dtype != torch.float32 or noise.device != dev:
+            raise ValueError(f"noise must be fp32 [{num_samples}, {B}, {V}] on {dev}")
+        noise = noise.contiguous()
+        flags |= _lib.FLAG_EXT_NOISE
+        noise_ptr, noise_ld = noise.data_ptr(), V
+
+    logits = None
+    if return_logits:
+        logits = torch.empty((B, V), dtype=torch.float32, device=dev)
+        flags |= _lib.FLAG_RETURN_LOGITS
+    if kernel == "gemv":
+        flags |= _lib.FLAG_FORCE_GEMV
+    elif kernel == "mma":
+        flags |= _lib.FLAG_FORCE_MMA
+    elif kernel is not None:
+        raise ValueError('kernel must be None, "gemv" or "mma"')
+
+    v_begin = 0
+    if tp.size > 1:
+        from .tensor_parallel import get_exchange
+
+        exchange = get_exchange(tp, dev)
+        v_begin = exchange.vocab_offset(V)
+    out = torch.empty((B, num_samples), dtype=torch.int64, device=dev)
+    need_vals = return_values or tp.size > 1
+    vals = torch.empty((B, num_samples), dtype=torch.float32, device=dev) if need_vals else None
+
+    stream = torch.cuda.current_stream(dev)
+    nbytes = _lib.query_workspace(V, D, B, num_samples)
+    ws = _workspace(dev, stream.cuda_stream, nbytes)
+    status = _status_word(dev)
+    with torch.cuda.device(dev):
+        rc = lib.fmms_sample(
+            weights.data_ptr(), hidden_states.data_ptr(), temp_ptr, temp_stride, V, D, B, num_samples,
+            int(seed) & 0xFFFFFFFFFFFFFFFF, v_begin, flags, noise_ptr, noise_ld,
+            logits.data_ptr() if logits is not None else None, out.data_ptr(),
+            vals.data_ptr() if vals is not None else None, ws.data_ptr(), ws.numel(),
+            status.data_ptr(), stream.cuda_stream,
+        )
+    _lib.check(rc, "fmms_sample")
+
+    if tp.size > 1:
+        out, vals = exchange.reduce(out, vals)
+
+    result = (out,)
+    if return_logits:
+        result += (logits,)
+    if return_values:
+        result += (vals,)
+    return result[0] if len(result) == 1 else result
+
+
+# The reference's name for the same entry point (core.py:224).
+fused_mm_sample_triton = fused_mm_sample
+
+
+class Sampler(Protocol):
+    """core.py:658-663."""
+
+    def prepare(self) -> "Sampler": ...
+
+    def sample(self, **kwargs) -> torch.Tensor: ...
+
+
+@dataclass
+class SimpleSampler:
+    """core.py:666-674."""
+
+    fn: Callable[..., torch.Tensor]
+
+    def prepare(self) -> "SimpleSampler":
+        return self
+
+    def sample(self, **kwargs) -> torch.Tensor:
+        return self.fn(**kwargs)
+
+
+PROVIDERS = (
+    "fused-b200",
+    "fused-triton",
+    "fused-triton-p2p-no-overlap",
+    "fused-triton-ret-logits",
+    "fused-triton-greedy",
+)
+
+
+def get_sampler(provider: str, weights: torch.Tensor) -> Sampler:
+    """Provider registry restricted to the fused path (core.py:744-767).
+
+    The reference's names for its fused kernel resolve to the CUDA
+    implementation, with the same default ``seed=0``; every other provider of
+    the reference (torch, FlashInfer, Helion, top-k, JL baselines) is outside
+    this library and raises ``NotImplementedError``.
+    """
+    if provider in ("fused-b200", "fused-triton"):
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, **kw}))
+    if provider == "fused-triton-p2p-no-overlap":
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "p2p_no_overlap": True, **kw}))
+    if provider == "fused-triton-ret-logits":
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "return_logits": True, **kw})[0])
+    if provider == "fused-triton-greedy":
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "greedy_sampling": True, **kw}))
+    raise NotImplementedError(f"Unknown provider: {provider} (this library implements {PROVIDERS})")

@@ -1,0 +1,349 @@
+// C ABI of the fused LM-head sampling library (see include/fmms_b200.h): argument
+// checks, kernel selection, TMA descriptor cache and launches.  No torch types, no
+// allocation on the sampling path, no synchronisation.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <vector>
+
+#include "../../include/fmms_b200.h"
+#include "fmms_common.cuh"
+#include "fmms_gemv.cuh"
+#include "fmms_umma.cuh"
+
+namespace fmms {
+
+constexpr int kVersion = 1000;
+constexpr int kMaxParts = 320;      // upper bound on candidate rows in the workspace (2 per persistent CTA)
+constexpr int kMaxDevices = 16;
+constexpr int kGemvAutoMaxBatch = 4;  // auto-dispatch: batches up to this use the weight-streaming kernel
+
+static thread_local int g_last_path = FMMS_PATH_NONE;
+
+struct DeviceInfo {
+  bool ready = false;
+  int num_sms = 0;
+  int cc_major = 0;
+  int max_smem_optin = 0;
+  bool gemv_attr[kGemvMaxBatch + 1] = {};
+  bool umma_attr[8] = {};
+};
+
+static std::mutex g_mu;
+static DeviceInfo g_dev[kMaxDevices];
+
+static int device_info(DeviceInfo** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return kErrCuda;
+  if (dev < 0 || dev >= kMaxDevices) return kErrUnsupported;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!d.ready) {
+      if (cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return kErrCuda;
+      if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return kErrCuda;
+      if (cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return kErrCuda;
+      d.ready = true;
+    }
+  }
+  *out = &d;
+  return kOk;
+}
+
+// ---- TMA descriptors ------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!tried) {
+      void* p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+          q == cudaDriverEntryPointSuccess)
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+      tried = true;
+    }
+  }
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols;
+  int box_rows, box_cols, swizzle;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows &&
+           box_cols == o.box_cols && swizzle == o.swizzle;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+};
+static std::vector<MapEntry> g_maps;
+
+// Row-major [rows, cols] bf16 matrix, box = box_rows x box_cols, out-of-range elements read as zero.
+static int get_tensor_map(const void* ptr, long long rows, long long cols, int box_rows, int box_cols,
+                          CUtensorMapSwizzle swz, CUtensorMap* out) {
+  MapKey key{ptr, rows, cols, box_rows, box_cols, (int)swz};
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (const MapEntry& e : g_maps)
+      if (e.key == key) {
+        *out = e.map;
+        return kOk;
+      }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return kErrCuda;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return kErrCuda;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_maps.size() >= 64) g_maps.erase(g_maps.begin());
+    g_maps.push_back(MapEntry{key, m});
+  }
+  *out = m;
+  return kOk;
+}
+
+// ---- GEMV launch ----------------------------------------------------------------
+template <int NB>
+static int launch_gemv_nb(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
+                          cudaStream_t stream) {
+  if (!d.gemv_attr[NB]) {
+    if (cudaFuncSetAttribute(gemv_sample_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             d.max_smem_optin) != cudaSuccess)
+      return kErrCuda;
+    d.gemv_attr[NB] = true;
+  }
+  gemv_sample_kernel<NB><<<grid, kGemvThreads, smem, stream>>>(map, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+static int gemv_stages(const DeviceInfo& d, int NB, int D) {
+  int stages = kGemvMaxStages;
+  while (stages >= 3 && gemv_smem_bytes(NB, D, stages) > (size_t)d.max_smem_optin) --stages;
+  return stages >= 3 ? stages : 0;
+}
+
+static bool gemv_eligible(const DeviceInfo& d, int D, int B, int S) {
+  return B <= kGemvMaxBatch && (long long)B * S <= 32 && gemv_stages(d, B, D) > 0;
+}
+
+static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream_t stream) {
+  CUtensorMap map;
+  int rc = get_tensor_map(W, p.V, p.D, kGemvRows, kGemvCols, CU_TENSOR_MAP_SWIZZLE_NONE, &map);
+  if (rc != kOk) return -rc;
+  const int NB = p.B;
+  p.stages = gemv_stages(d, NB, p.D);
+  const size_t smem = gemv_smem_bytes(NB, p.D, p.stages);
+  const int groups = (p.V + kGemvRows - 1) / kGemvRows;
+  const int grid = groups < d.num_sms ? groups : d.num_sms;
+  switch (NB) {
+    case 1: rc = launch_gemv_nb<1>(d, map, p, grid, smem, stream); break;
+    case 2: rc = launch_gemv_nb<2>(d, map, p, grid, smem, stream); break;
+    case 3: rc = launch_gemv_nb<3>(d, map, p, grid, smem, stream); break;
+    case 4: rc = launch_gemv_nb<4>(d, map, p, grid, smem, stream); break;
+    case 5: rc = launch_gemv_nb<5>(d, map, p, grid, smem, stream); break;
+    case 6: rc = launch_gemv_nb<6>(d, map, p, grid, smem, stream); break;
+    case 7: rc = launch_gemv_nb<7>(d, map, p, grid, smem, stream); break;
+    case 8: rc = launch_gemv_nb<8>(d, map, p, grid, smem, stream); break;
+    default: return -kErrUnsupported;
+  }
+  if (rc != kOk) return -rc;
+  return grid;  // > 0: number of candidate rows written
+}
+
+// ---- tensor-core launch -----------------------------------------------------------
+template <int MT>
+static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wm, const CUtensorMap& hm, SampleParams& p,
+                          const UmmaPlan& pl, cudaStream_t stream) {
+  if (!d.umma_attr[MT]) {
+    if (cudaFuncSetAttribute(umma_sample_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             d.max_smem_optin) != cudaSuccess)
+      return kErrCuda;
+    d.umma_attr[MT] = true;
+  }
+  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wm, hm, p, pl.nt_cap, pl.tiles_total, pl.h_rows);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
+  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin);
+  if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
+  CUtensorMap wm, hm;
+  int rc = get_tensor_map(W, p.V, p.D, pl.tile_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wm);
+  if (rc != kOk) return -rc;
+  rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &hm);
+  if (rc != kOk) return -rc;
+  p.stages = pl.stages;
+  p.tile_rows = pl.tile_rows;
+  rc = pl.mt == 1 ? launch_umma_mt<1>(d, wm, hm, p, pl, stream) : launch_umma_mt<2>(d, wm, hm, p, pl, stream);
+  if (rc != kOk) return -rc;
+  return pl.grid * 2;
+}
+
+}  // namespace fmms
+
+using namespace fmms;
+
+extern "C" {
+
+int fmms_version(void) { return kVersion; }
+
+const char* fmms_strerror(int status) {
+  switch (status) {
+    case FMMS_OK: return "ok";
+    case FMMS_ERR_TIMEOUT: return "a bounded device-side wait timed out";
+    case FMMS_ERR_BAD_ARG: return "bad argument";
+    case FMMS_ERR_UNSUPPORTED: return "unsupported shape or alignment";
+    case FMMS_ERR_WORKSPACE: return "workspace missing or too small";
+    case FMMS_ERR_CUDA: return "CUDA call failed";
+    case FMMS_ERR_ARCH: return "device is not compute capability 10.x (sm_100a)";
+    default: return "unknown status";
+  }
+}
+
+int fmms_num_sms(int* num_sms) {
+  if (!num_sms) return FMMS_ERR_BAD_ARG;
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != kOk) return rc;
+  *num_sms = d->num_sms;
+  return FMMS_OK;
+}
+
+int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes) {
+  if (!bytes || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
+  *bytes = (size_t)kMaxParts * (size_t)B * (size_t)S * 8 + 256;
+  return FMMS_OK;
+}
+
+int fmms_last_path(void) { return g_last_path; }
+
+int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_smem_bytes, int* plan) {
+  if (!plan || V_local <= 0 || D <= 0 || B <= 0 || S <= 0 || num_sms <= 0 || max_smem_bytes <= 0)
+    return FMMS_ERR_BAD_ARG;
+  if (D % 8 != 0 || B > 256) return FMMS_ERR_UNSUPPORTED;
+  DeviceInfo d;
+  d.num_sms = num_sms;
+  d.max_smem_optin = max_smem_bytes;
+  const bool can_gemv = gemv_eligible(d, D, B, S);
+  bool use_gemv = can_gemv && B <= kGemvAutoMaxBatch;
+  if (flags & FMMS_FLAG_FORCE_GEMV) {
+    if (!can_gemv) return FMMS_ERR_UNSUPPORTED;
+    use_gemv = true;
+  }
+  if (flags & FMMS_FLAG_FORCE_MMA) use_gemv = false;
+  for (int i = 0; i < 8; ++i) plan[i] = 0;
+  if (use_gemv) {
+    const int groups = (V_local + kGemvRows - 1) / kGemvRows;
+    plan[0] = FMMS_PATH_GEMV;
+    plan[1] = groups < num_sms ? groups : num_sms;
+    plan[2] = kGemvRows;
+    plan[3] = groups;
+    plan[4] = gemv_stages(d, B, D);
+    plan[5] = 1;
+    plan[6] = (int)gemv_smem_bytes(B, D, plan[4]);
+    plan[7] = plan[1];
+  } else {
+    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes);
+    plan[0] = FMMS_PATH_MMA;
+    plan[1] = pl.grid;
+    plan[2] = pl.tile_rows;
+    plan[3] = pl.tiles_total;
+    plan[4] = pl.stages;
+    plan[5] = pl.mt;
+    plan[6] = (int)pl.smem;
+    plan[7] = pl.grid * 2;
+  }
+  return FMMS_OK;
+}
+
+int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                int* status_dev, void* stream_v) {
+  g_last_path = FMMS_PATH_NONE;
+  if (!W_bf16 || !H_bf16 || !out_idx || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
+  const bool greedy = flags & FMMS_FLAG_GREEDY, ext = flags & FMMS_FLAG_EXT_NOISE;
+  if (!greedy && !temperature) return FMMS_ERR_BAD_ARG;
+  if (temp_stride != 0 && temp_stride != 1) return FMMS_ERR_BAD_ARG;
+  if (ext && !greedy && (!ext_noise || noise_ld < V_local)) return FMMS_ERR_BAD_ARG;
+  if ((flags & FMMS_FLAG_RETURN_LOGITS) && !logits_out) return FMMS_ERR_BAD_ARG;
+  if ((flags & FMMS_FLAG_FORCE_GEMV) && (flags & FMMS_FLAG_FORCE_MMA)) return FMMS_ERR_BAD_ARG;
+  if (v_global_offset < 0) return FMMS_ERR_BAD_ARG;
+  if (D % 8 != 0 || ((uintptr_t)W_bf16 & 15) || ((uintptr_t)H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
+  if (B > 256) return FMMS_ERR_UNSUPPORTED;
+  size_t need = 0;
+  fmms_query_workspace(V_local, D, B, S, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return FMMS_ERR_WORKSPACE;
+
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != kOk) return rc;
+  if (d->cc_major != 10) return FMMS_ERR_ARCH;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+
+  SampleParams p{};
+  p.H = reinterpret_cast<const __nv_bfloat16*>(H_bf16);
+  p.temperature = temperature;
+  p.temp_stride = temp_stride;
+  p.V = V_local;
+  p.D = D;
+  p.B = B;
+  p.S = S;
+  p.seed = seed;
+  p.v_offset = v_global_offset;
+  p.flags = flags;
+  p.ext_noise = ext_noise;
+  p.noise_ld = noise_ld;
+  p.logits_out = logits_out;
+  p.cand_val = reinterpret_cast<float*>(workspace);
+  p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
+  p.status_dev = status_dev;
+
+  const bool can_gemv = gemv_eligible(*d, D, B, S);
+  bool use_gemv;
+  if (flags & FMMS_FLAG_FORCE_GEMV) {
+    if (!can_gemv) return FMMS_ERR_UNSUPPORTED;
+    use_gemv = true;
+  } else if (flags & FMMS_FLAG_FORCE_MMA) {
+    use_gemv = false;
+  } else {
+    use_gemv = can_gemv && B <= kGemvAutoMaxBatch;
+  }
+
+  int parts;
+  if (use_gemv) {
+    parts = launch_gemv(*d, W_bf16, p, stream);
+    g_last_path = FMMS_PATH_GEMV;
+  } else {
+    parts = launch_umma(*d, W_bf16, H_bf16, p, stream);
+    g_last_path = FMMS_PATH_MMA;
+  }
+  if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
+
+  const int n = B * S;
+  reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.cand_val, p.cand_idx, parts, B, S,
+                                                                 v_global_offset, out_idx, out_val);
+  return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+}  // extern "C"

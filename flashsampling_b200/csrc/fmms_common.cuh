@@ -1,0 +1,213 @@
+// Device-side building blocks shared by the sampling kernels: the counter-based
+// noise stream, candidate ordering, and thin wrappers over the sm_100a PTX used
+// for mbarriers, TMA (cp.async.bulk.tensor) and tcgen05/TMEM.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmms {
+
+// ------------------------------------------------------------------------------------
+// status / flags (mirrors include/fmms_b200.h)
+// ------------------------------------------------------------------------------------
+constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kErrWorkspace = 4,
+              kErrCuda = 5, kErrArch = 6;
+constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
+              kFlagForceMma = 16;
+
+constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"
+
+// Bounded waits: a wait gives up after this many nanoseconds of wall-clock time,
+// records kErrTimeout and lets the kernel run to its end on whatever data it has.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// ------------------------------------------------------------------------------------
+// Noise: Philox-4x32-10 keyed by (seed + sample), counter = (v >> 2, b, v >> 34, 0)
+// ------------------------------------------------------------------------------------
+constexpr uint32_t kPhiloxM0 = 0xD2511F53u, kPhiloxM1 = 0xCD9E8D57u;
+constexpr uint32_t kPhiloxW0 = 0x9E3779B9u, kPhiloxW1 = 0xBB67AE85u;
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(kPhiloxM0, c.x), lo0 = kPhiloxM0 * c.x;
+    const uint32_t hi1 = __umulhi(kPhiloxM1, c.z), lo1 = kPhiloxM1 * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += kPhiloxW0;
+    k.y += kPhiloxW1;
+  }
+  return c;
+}
+
+// The four 32-bit words for global vocabulary ids 4q .. 4q+3 of row b, draw s.
+__device__ __forceinline__ uint4 noise_block(unsigned long long seed, int s, int b,
+                                             unsigned long long v_quad) {
+  const unsigned long long stream = seed + (unsigned long long)s;
+  return philox4x32_10(make_uint4((uint32_t)v_quad, (uint32_t)b, (uint32_t)(v_quad >> 32), 0u),
+                       make_uint2((uint32_t)stream, (uint32_t)(stream >> 32)));
+}
+
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Standard Gumbel variate from 32 random bits.  w = (r + 0.5) 2^-32; the unit
+// exponential E = -log1p(-w) is a cubic in w below 2^-7 (fp32 keeps the full
+// relative precision of small w, which is the winning upper tail of the Gumbel)
+// and -ln(1 - w) above; G = -ln E.  w == 1 after rounding gives G = -inf, which
+// simply never wins.
+__device__ __forceinline__ float gumbel_from_bits(uint32_t r) {
+  constexpr float kLn2 = 0.6931471805599453f;
+  const float w = fmaf(__uint2float_rn(r), 0x1p-32f, 0x1p-33f);
+  const float e_small = w * fmaf(w, fmaf(w, 0.3333333333f, 0.5f), 1.0f);
+  const float e_big = -kLn2 * lg2_approx(1.0f - w);
+  const float e = (w < 0x1p-7f) ? e_small : e_big;
+  return -kLn2 * lg2_approx(e);
+}
+
+__device__ __forceinline__ uint32_t pick_word(const uint4& q, uint32_t i) {
+  return i == 0 ? q.x : (i == 1 ? q.y : (i == 2 ? q.z : q.w));
+}
+
+// Candidate order: larger value wins, equal values resolve to the lower index.
+__device__ __forceinline__ bool cand_better(float v1, int i1, float v2, int i2) {
+  return (v1 > v2) || (v1 == v2 && i1 < i2);
+}
+
+__device__ __forceinline__ void cand_merge(float& v, int& i, float v2, int i2) {
+  if (cand_better(v2, i2, v, i)) {
+    v = v2;
+    i = i2;
+  }
+}
+
+__device__ __forceinline__ void warp_cand_allreduce(float& v, int& i) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, v, off);
+    const int i2 = __shfl_xor_sync(0xffffffffu, i, off);
+    cand_merge(v, i, v2, i2);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded mbarrier wait.  `abort_flag` lives in shared memory: once any wait of
+// the CTA has timed out every later wait returns at once, so the kernel drains
+// instead of stacking time-outs.  Returns false on time-out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_dev) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status_dev) atomicExch(status_dev, kErrTimeout);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Bounded wait that ignores the abort flag (used while draining after a time-out).
+__device__ __forceinline__ bool mbar_wait_plain(uint64_t* bar, uint32_t parity,
+                                                unsigned long long limit_ns) {
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+
+// 2-D tiled TMA load, completion signalled on an mbarrier (bytes of the full box).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const void* tmap, int x, int y,
+                                                 uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+}  // namespace fmms

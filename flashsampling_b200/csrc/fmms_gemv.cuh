@@ -1,0 +1,297 @@
+// Small-batch weight-streaming kernel (batch rows <= 8).
+//
+// A persistent grid of one CTA per SM walks contiguous ranges of 32-row groups of
+// W[V, D].  A producer warp streams 32 x 256 bf16 boxes (16 KiB) of W through a
+// shared-memory ring with TMA (cp.async.bulk.tensor) and mbarriers; eight consumer
+// warps each own four rows of the group and accumulate fp32 dot products against
+// the hidden states, which sit in shared memory for the whole kernel.  When a group
+// is complete the sums are reduced across the warp, scaled by 1/T, perturbed with
+// Gumbel noise and folded into a running (max, index) per (row b, draw s) that
+// lives in registers for the whole CTA; one candidate per (b, s) per CTA reaches
+// global memory.
+#pragma once
+
+#include <cuda.h>
+
+#include "fmms_common.cuh"
+
+namespace fmms {
+
+constexpr int kGemvConsumerWarps = 8;
+constexpr int kGemvRowsPerWarp = 4;
+constexpr int kGemvRows = kGemvConsumerWarps * kGemvRowsPerWarp;  // 32 rows per group
+constexpr int kGemvCols = 256;                                    // columns per stage
+constexpr int kGemvStageBytes = kGemvRows * kGemvCols * 2;        // 16 KiB
+constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer warp
+constexpr int kGemvMaxBatch = 8;
+constexpr int kGemvItemsPerLane = 4;  // (row, b, s) items a lane may own: 4 * NB * S <= 128
+constexpr int kGemvMaxStages = 12;
+
+struct SampleParams {
+  const __nv_bfloat16* H;    // [B, D]
+  const float* temperature;  // [1] or [B]
+  int temp_stride;           // 0 or 1
+  int V, D, B, S;
+  unsigned long long seed;
+  long long v_offset;        // global vocabulary id of row 0
+  int flags;
+  const float* ext_noise;    // [S, B, noise_ld]
+  long long noise_ld;
+  float* logits_out;         // [B, V]
+  float* cand_val;           // [gridDim.x, S * B]
+  int* cand_idx;             // [gridDim.x, S * B]
+  int* status_dev;
+  int stages;                // shared-memory ring depth
+  int tile_rows;             // tensor-core path: vocabulary rows per tile
+  int tiles_per_cta;         // tensor-core path
+};
+
+__host__ __device__ inline int gemv_dpad(int D) { return (D + kGemvCols - 1) / kGemvCols * kGemvCols; }
+
+__host__ __device__ inline size_t gemv_smem_bytes(int NB, int D, int stages) {
+  return (size_t)stages * kGemvStageBytes + (size_t)NB * gemv_dpad(D) * 2 + 16 * (size_t)stages +
+         kGemvConsumerWarps * 32 * 8 + 16;
+}
+
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t x) {
+  return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kGemvThreads, 1)
+gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int stages = p.stages;
+  const int KC = (p.D + kGemvCols - 1) / kGemvCols;
+  const int Dpad = KC * kGemvCols;
+
+  uint8_t* w_tiles = smem;
+  __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(smem + (size_t)stages * kGemvStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(hs) + (size_t)NB * Dpad * 2);
+  uint64_t* empty_bar = full_bar + stages;
+  float* red_val = reinterpret_cast<float*>(empty_bar + stages);
+  int* red_idx = reinterpret_cast<int*>(red_val + kGemvConsumerWarps * 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red_idx + kGemvConsumerWarps * 32);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  // contiguous range of row groups of this CTA
+  const int groups_total = (p.V + kGemvRows - 1) / kGemvRows;
+  const int base = groups_total / (int)gridDim.x, rem = groups_total % (int)gridDim.x;
+  const int cta = blockIdx.x;
+  const int g_begin = cta * base + min(cta, rem);
+  const int g_end = g_begin + base + (cta < rem ? 1 : 0);
+
+  if (tid == 0) {
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], kGemvConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  // hidden states -> shared memory, zero padded to [NB][Dpad]
+  {
+    const int chunks_per_row = Dpad / 8;
+    const int d_chunks = p.D / 8;  // D % 8 == 0 is checked on the host
+    for (int i = tid; i < NB * chunks_per_row; i += kGemvThreads) {
+      const int b = i / chunks_per_row, c = i - b * chunks_per_row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (b < p.B && c < d_chunks) v = *reinterpret_cast<const uint4*>(p.H + (size_t)b * p.D + c * 8);
+      *reinterpret_cast<uint4*>(hs + (size_t)b * Dpad + c * 8) = v;
+    }
+  }
+  __syncthreads();
+
+  if (warp == kGemvConsumerWarps) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&w_map);
+      const uint64_t pol = policy_evict_first();
+      int it = 0;
+      for (int g = g_begin; g < g_end; ++g) {
+        for (int kc = 0; kc < KC; ++kc, ++it) {
+          const int st = it % stages;
+          const uint32_t n = (uint32_t)(it / stages);
+          if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) break;
+          mbar_arrive_expect_tx(&full_bar[st], kGemvStageBytes);
+          tma_load_2d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, kc * kGemvCols,
+                           g * kGemvRows, &full_bar[st], pol);
+        }
+        if (*abort_flag) break;
+      }
+      if (*abort_flag) {
+        // A wait ran out somewhere: before the CTA may retire, give the copies that
+        // are still in flight a bounded chance to land in shared memory.
+        for (int st = 0; st < min(it, stages); ++st) {
+          const int last_it = ((it - 1 - st) / stages) * stages + st;
+          mbar_wait_plain(&full_bar[st], (uint32_t)(last_it / stages) & 1u, 100000000ull);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const bool greedy = (p.flags & kFlagGreedy) != 0;
+  const bool ext = (p.flags & kFlagExtNoise) != 0;
+  const bool ret_logits = (p.flags & kFlagReturnLogits) != 0;
+  const int n_items = kGemvRowsPerWarp * NB * p.S;
+
+  int item_r[kGemvItemsPerLane], item_b[kGemvItemsPerLane], item_s[kGemvItemsPerLane];
+  bool item_ok[kGemvItemsPerLane];
+  float item_invT[kGemvItemsPerLane], best_val[kGemvItemsPerLane];
+  int best_idx[kGemvItemsPerLane];
+#pragma unroll
+  for (int j = 0; j < kGemvItemsPerLane; ++j) {
+    const int i = j * 32 + lane;
+    item_r[j] = i & 3;
+    item_b[j] = (i >> 2) % NB;
+    item_s[j] = (i >> 2) / NB;
+    item_ok[j] = (i < n_items) && (item_b[j] < p.B);
+    item_invT[j] = 1.0f;
+    if (item_ok[j] && !greedy) item_invT[j] = 1.0f / p.temperature[(size_t)item_b[j] * p.temp_stride];
+    best_val[j] = -INFINITY;
+    best_idx[j] = kIdxNone;
+  }
+
+  int it = 0;
+  for (int g = g_begin; g < g_end; ++g) {
+    float2 acc[kGemvRowsPerWarp][NB];
+#pragma unroll
+    for (int r = 0; r < kGemvRowsPerWarp; ++r)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) acc[r][b] = make_float2(0.f, 0.f);
+
+    for (int kc = 0; kc < KC; ++kc, ++it) {
+      const int st = it % stages;
+      const uint32_t n = (uint32_t)(it / stages);
+      mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev);
+
+      float2 hreg[NB][4];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(hs + (size_t)b * Dpad + kc * kGemvCols + lane * 8);
+        hreg[b][0] = bf16x2_to_float2(hv.x);
+        hreg[b][1] = bf16x2_to_float2(hv.y);
+        hreg[b][2] = bf16x2_to_float2(hv.z);
+        hreg[b][3] = bf16x2_to_float2(hv.w);
+      }
+      const uint8_t* tile = w_tiles + (size_t)st * kGemvStageBytes + (size_t)(warp * kGemvRowsPerWarp) * (kGemvCols * 2) + lane * 16;
+#pragma unroll
+      for (int r = 0; r < kGemvRowsPerWarp; ++r) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * (kGemvCols * 2));
+        const float2 w0 = bf16x2_to_float2(wv.x), w1 = bf16x2_to_float2(wv.y);
+        const float2 w2 = bf16x2_to_float2(wv.z), w3 = bf16x2_to_float2(wv.w);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          float2 a = acc[r][b];
+          a = __ffma2_rn(w0, hreg[b][0], a);
+          a = __ffma2_rn(w1, hreg[b][1], a);
+          a = __ffma2_rn(w2, hreg[b][2], a);
+          a = __ffma2_rn(w3, hreg[b][3], a);
+          acc[r][b] = a;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[st]);
+    }
+
+    // warp-wide sums: every lane ends up with all 4 * NB logits of the warp's rows
+    float sum[kGemvRowsPerWarp][NB];
+#pragma unroll
+    for (int r = 0; r < kGemvRowsPerWarp; ++r)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float x = acc[r][b].x + acc[r][b].y;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+        sum[r][b] = x;
+      }
+
+    const int v_warp = g * kGemvRows + warp * kGemvRowsPerWarp;
+#pragma unroll
+    for (int j = 0; j < kGemvItemsPerLane; ++j) {
+      const int v = v_warp + item_r[j];
+      if (item_ok[j] && v < p.V) {
+        float val = 0.f;
+#pragma unroll
+        for (int r = 0; r < kGemvRowsPerWarp; ++r)
+#pragma unroll
+          for (int b = 0; b < NB; ++b)
+            if (item_r[j] == r && item_b[j] == b) val = sum[r][b];
+        if (ret_logits && item_s[j] == 0) p.logits_out[(size_t)item_b[j] * p.V + v] = val;
+        float y;
+        if (greedy) {
+          y = val;
+        } else if (ext) {
+          y = fmaf(val, item_invT[j], p.ext_noise[((size_t)item_s[j] * p.B + item_b[j]) * p.noise_ld + v]);
+        } else {
+          const unsigned long long vg = (unsigned long long)(p.v_offset + v);
+          const uint4 q = noise_block(p.seed, item_s[j], item_b[j], vg >> 2);
+          y = fmaf(val, item_invT[j], gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+        }
+        if (y > best_val[j]) {
+          best_val[j] = y;
+          best_idx[j] = v;
+        }
+      }
+    }
+  }
+
+  // ---- CTA-level reduction of the running candidates: rows (2 shuffles), warps (smem) ----
+#pragma unroll
+  for (int j = 0; j < kGemvItemsPerLane; ++j) {
+#pragma unroll
+    for (int off = 1; off <= 2; off <<= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, best_val[j], off);
+      const int i2 = __shfl_xor_sync(0xffffffffu, best_idx[j], off);
+      cand_merge(best_val[j], best_idx[j], v2, i2);
+    }
+  }
+  const int n_slots = NB * p.S;  // <= 32, slot = b + NB * s
+#pragma unroll
+  for (int j = 0; j < kGemvItemsPerLane; ++j) {
+    const int i = j * 32 + lane;
+    if ((i & 3) == 0 && (i >> 2) < n_slots) {
+      red_val[warp * 32 + (i >> 2)] = best_val[j];
+      red_idx[warp * 32 + (i >> 2)] = best_idx[j];
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory");
+  if (tid < n_slots) {
+    float bv = red_val[tid];
+    int bi = red_idx[tid];
+#pragma unroll
+    for (int w = 1; w < kGemvConsumerWarps; ++w) cand_merge(bv, bi, red_val[w * 32 + tid], red_idx[w * 32 + tid]);
+    const int b = tid % NB, s = tid / NB;
+    if (b < p.B) {
+      const size_t o = (size_t)blockIdx.x * (p.S * p.B) + (size_t)s * p.B + b;
+      p.cand_val[o] = bv;
+      p.cand_idx[o] = bi;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Cross-CTA reduction: one thread per (b, s) scans the per-CTA candidates.
+// ---------------------------------------------------------------------------------
+__global__ void reduce_candidates_kernel(const float* __restrict__ cand_val,
+                                         const int* __restrict__ cand_idx, int parts, int B, int S,
+                                         long long v_offset, long long* __restrict__ out_idx,
+                                         float* __restrict__ out_val) {
+  const int item = blockIdx.x * blockDim.x + threadIdx.x;  // s * B + b
+  const int n = B * S;
+  if (item >= n) return;
+  float bv = -INFINITY;
+  int bi = kIdxNone;
+  for (int pidx = 0; pidx < parts; ++pidx) {
+    cand_merge(bv, bi, cand_val[(size_t)pidx * n + item], cand_idx[(size_t)pidx * n + item]);
+  }
+  const int s = item / B, b = item - s * B;
+  out_idx[(size_t)b * S + s] = v_offset + (bi == kIdxNone ? 0 : bi);
+  if (out_val) out_val[(size_t)b * S + s] = bv;
+}
+
+}  // namespace fmms

@@ -1,0 +1,410 @@
+// Tensor-core kernel: tcgen05.mma with TMEM accumulators, fed by TMA.
+//
+// Orientation: the batch sits on the MMA M axis (128 TMEM lanes = 128 hidden-state
+// rows, zero-extended) and the vocabulary on the N axis (up to 256 TMEM columns per
+// tile).  D[128, NT] = Hs[128, 64] * Wt[NT, 64]^T per 64-wide slice of the hidden
+// dimension, both operands K-major in shared memory with the 128-byte swizzle that
+// TMA writes and the MMA descriptor names.  An epilogue thread therefore owns ONE
+// batch row and walks vocabulary columns in order: the Gumbel-max scan is a running
+// (max, index) in two registers, with no cross-lane traffic until the kernel ends.
+//
+// Warp roles (384 threads, one CTA per SM, persistent over a contiguous range of
+// vocabulary tiles):
+//   warp 0      TMA producer: W tile + hidden-state tile(s) per pipeline stage
+//   warp 1      TMEM allocation, then one elected thread issues tcgen05.mma/commit
+//   warps 4-11  epilogue: tcgen05.ld -> scale, noise, running argmax.  TMEM
+//               accumulators are multi-buffered so the epilogue of tile i overlaps
+//               the mainloop of tile i+1.
+// Batches above 128 use two M tiles that share every W tile (MT = 2).
+#pragma once
+
+#include <cuda.h>
+
+#include "fmms_common.cuh"
+#include "fmms_gemv.cuh"  // SampleParams
+
+namespace fmms {
+
+constexpr int kUmmaThreads = 384;
+constexpr int kUmmaEpiWarp0 = 4;       // first epilogue warp
+constexpr int kUmmaEpiWarps = 8;       // two warpgroups
+constexpr int kUmmaBK = 64;            // hidden-dimension slice per stage (128 B of bf16)
+constexpr int kUmmaWTileBytes = 256 * 128;  // room for a 256-row W tile per stage
+constexpr int kUmmaHTileBytes = 128 * 128;  // one 128-row hidden-state tile
+constexpr int kTmemCols = 512;
+
+struct UmmaPlan {
+  int grid;         // persistent CTAs
+  int tile_rows;    // NT: vocabulary rows per tile (multiple of 16, <= nt_cap)
+  int nt_cap;       // TMEM columns reserved per accumulator (256 or 128)
+  int tiles_total;  // ceil(V / NT)
+  int stages;       // shared-memory ring depth
+  int h_rows;       // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
+  int mt;           // M tiles (1 or 2)
+  size_t smem;
+};
+
+__host__ __device__ inline size_t umma_stage_bytes(int mt) { return (size_t)kUmmaWTileBytes + (size_t)mt * kUmmaHTileBytes; }
+
+__host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem) {
+  UmmaPlan pl{};
+  pl.mt = B > 128 ? 2 : 1;
+  pl.nt_cap = pl.mt == 1 ? 256 : 128;
+  int grid = (V + 15) / 16;
+  if (grid > num_sms) grid = num_sms;
+  pl.grid = grid;
+  // Tile height: minimise the rows the busiest CTA walks (tiles are dealt out in
+  // contiguous, near-equal ranges).  Short tiles re-read the hidden-state operand
+  // too often for the shared-memory bandwidth, so large vocabularies keep NT high.
+  const int nt_floor = pl.mt == 1 ? 128 : 96;
+  const int nt_min = ((long long)V >= (long long)grid * nt_floor) ? nt_floor : 16;
+  long long best_cost = -1;
+  for (int nt = nt_min; nt <= pl.nt_cap; nt += 16) {
+    const int tiles = (V + nt - 1) / nt;
+    const long long cost = (long long)((tiles + grid - 1) / grid) * nt;
+    if (best_cost < 0 || cost <= best_cost) {  // ties: prefer the larger tile
+      best_cost = cost;
+      pl.tile_rows = nt;
+      pl.tiles_total = tiles;
+    }
+  }
+  if (pl.tiles_total < pl.grid) pl.grid = pl.tiles_total;
+  pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
+  const size_t fixed = 1024 /*barriers etc.*/ + 1024 /*alignment slack*/;
+  int stages = 6;
+  while (stages > 2 && stages * umma_stage_bytes(pl.mt) + fixed > (size_t)max_smem) --stages;
+  pl.stages = stages;
+  pl.smem = stages * umma_stage_bytes(pl.mt) + fixed;
+  return pl;
+}
+
+// ---- tcgen05 wrappers ----------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
+__host__ __device__ inline uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- the kernel ------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap h_map,
+                   const SampleParams p, const int nt_cap, const int tiles_total, const int h_rows) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int stages = p.stages;
+  const int NT = p.tile_rows;
+  const size_t stage_bytes = umma_stage_bytes(MT);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* acc_full = empty_bar + stages;
+  uint64_t* acc_empty = acc_full + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int acc_stages = kTmemCols / (MT * nt_cap);
+  const int KB = (p.D + kUmmaBK - 1) / kUmmaBK;
+
+  // contiguous tile range of this CTA
+  const int base = tiles_total / (int)gridDim.x, rem = tiles_total % (int)gridDim.x;
+  const int cta = blockIdx.x;
+  const int t_begin = cta * base + min(cta, rem);
+  const int n_tiles = base + (cta < rem ? 1 : 0);
+
+  if (tid == 0) {
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], kUmmaEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  // candidate rows of this CTA start as "none": two rows (one per epilogue warpgroup)
+  {
+    const int n = 2 * p.S * p.B;
+    float* cv = p.cand_val + (size_t)cta * n;
+    int* ci = p.cand_idx + (size_t)cta * n;
+    for (int i = tid; i < n; i += kUmmaThreads) {
+      cv[i] = -INFINITY;
+      ci[i] = kIdxNone;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&w_map);
+      prefetch_tmap(&h_map);
+      const uint64_t pol_w = policy_evict_first(), pol_h = policy_evict_last();
+      const uint32_t tx = (uint32_t)NT * 128u + (uint32_t)MT * (uint32_t)h_rows * 128u;
+      int it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int v0 = (t_begin + t) * NT;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int st = it % stages;
+          const uint32_t n = (uint32_t)(it / stages);
+          if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sw = smem + st * stage_bytes;
+          mbar_arrive_expect_tx(&full_bar[st], tx);
+          tma_load_2d_hint(sw, &w_map, kb * kUmmaBK, v0, &full_bar[st], pol_w);
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            tma_load_2d_hint(sw + kUmmaWTileBytes + m * kUmmaHTileBytes, &h_map, kb * kUmmaBK, m * 128,
+                             &full_bar[st], pol_h);
+        }
+      }
+      if (*abort_flag) {
+        for (int st = 0; st < min(it, stages); ++st) {
+          const int last_it = ((it - 1 - st) / stages) * stages + st;
+          mbar_wait_plain(&full_bar[st], (uint32_t)(last_it / stages) & 1u, 100000000ull);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(NT);
+      int it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int j = t % acc_stages;
+        const uint32_t un = (uint32_t)(t / acc_stages);
+        if (!mbar_wait(&acc_empty[j], (un & 1u) ^ 1u, abort_flag, p.status_dev)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int st = it % stages;
+          const uint32_t n = (uint32_t)(it / stages);
+          if (!mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sw = smem_u32(smem + st * stage_bytes);
+          const uint64_t bdesc = umma_smem_desc(sw);
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const uint64_t adesc = umma_smem_desc(sw + kUmmaWTileBytes + m * kUmmaHTileBytes);
+            const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
+#pragma unroll
+            for (int k = 0; k < kUmmaBK / 16; ++k) {
+              // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
+              umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty_bar[st]);  // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[j]);  // accumulator complete
+      }
+    }
+  } else if (warp >= kUmmaEpiWarp0) {
+    // -------------------------------- epilogue --------------------------------
+    const int ew = warp - kUmmaEpiWarp0;  // 0..7
+    const int wg = ew >> 2;               // epilogue warpgroup
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int m_tile = (MT == 2) ? wg : 0;
+    const int b = m_tile * 128 + quad * 32 + lane;
+    const bool row_ok = b < p.B;
+    const bool warp_ok = (m_tile * 128 + quad * 32) < p.B;
+    // column range of this warp inside a tile: MT = 1 splits the tile between the warpgroups
+    const int half = ((NT / 2) + 31) / 32 * 32;
+    const int c_begin = (MT == 2) ? 0 : (wg == 0 ? 0 : min(half, NT));
+    const int c_end = (MT == 2) ? NT : (wg == 0 ? min(half, NT) : NT);
+
+    const bool greedy = (p.flags & kFlagGreedy) != 0;
+    const bool ext = (p.flags & kFlagExtNoise) != 0;
+    const bool ret_logits = (p.flags & kFlagReturnLogits) != 0;
+    const bool quad_aligned = (p.v_offset & 3) == 0;
+    float invT = 1.0f;
+    if (row_ok && !greedy) invT = 1.0f / p.temperature[(size_t)b * p.temp_stride];
+    const int S = p.S;
+    const size_t slot_row = ((size_t)cta * 2 + wg) * ((size_t)S * p.B);
+
+    float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
+    int best_idx = kIdxNone;
+
+    for (int t = 0; t < n_tiles; ++t) {
+      const int j = t % acc_stages;
+      const uint32_t un = (uint32_t)(t / acc_stages);
+      if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
+      tc_fence_after();
+      if (warp_ok) {
+        const int v0 = (t_begin + t) * NT;
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
+        for (int s = 0; s < S; ++s) {
+          float bv = best_val;
+          int bi = best_idx;
+          if (S > 1) {
+            bv = -INFINITY;
+            bi = kIdxNone;
+          }
+          for (int c = c_begin; c < c_end; c += 32) {
+            uint32_t acc[32];
+            tmem_ld32(t_addr + (uint32_t)c, acc);
+            if (row_ok) {
+              const int vbase = v0 + c;
+              if (ret_logits && s == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (c + i < c_end && vbase + i < p.V)
+                    p.logits_out[(size_t)b * p.V + vbase + i] = __uint_as_float(acc[i]);
+              }
+              if (greedy) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const float y = __uint_as_float(acc[i]);
+                  if (c + i < c_end && vbase + i < p.V && y > bv) {
+                    bv = y;
+                    bi = vbase + i;
+                  }
+                }
+              } else if (ext) {
+                const float* nz = p.ext_noise + ((size_t)s * p.B + b) * p.noise_ld + vbase;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (c + i < c_end && vbase + i < p.V) {
+                    const float y = fmaf(__uint_as_float(acc[i]), invT, nz[i]);
+                    if (y > bv) {
+                      bv = y;
+                      bi = vbase + i;
+                    }
+                  }
+                }
+              } else if (quad_aligned) {
+                const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  const uint4 q = noise_block(p.seed, s, b, q0 + g);
+                  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int i = g * 4 + e;
+                    const float y = fmaf(__uint_as_float(acc[i]), invT, gumbel_from_bits(w[e]));
+                    if (c + i < c_end && vbase + i < p.V && y > bv) {
+                      bv = y;
+                      bi = vbase + i;
+                    }
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
+                  const uint4 q = noise_block(p.seed, s, b, vg >> 2);
+                  const float y = fmaf(__uint_as_float(acc[i]), invT, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+                  if (c + i < c_end && vbase + i < p.V && y > bv) {
+                    bv = y;
+                    bi = vbase + i;
+                  }
+                }
+              }
+            }
+          }
+          if (S > 1) {
+            if (row_ok) {
+              const size_t o = slot_row + (size_t)s * p.B + b;
+              if (bv > p.cand_val[o]) {  // later tiles have larger indices: strict compare keeps the lowest
+                p.cand_val[o] = bv;
+                p.cand_idx[o] = bi;
+              }
+            }
+          } else {
+            best_val = bv;
+            best_idx = bi;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[j]);
+    }
+    if (S == 1 && row_ok) {
+      p.cand_val[slot_row + b] = best_val;
+      p.cand_idx[slot_row + b] = best_idx;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fmms

@@ -1,0 +1,114 @@
+/*
+ * fmms_b200.h - C ABI of the B200 (sm_100a) fused LM-head sampling library.
+ *
+ * One pass over a bf16 LM-head weight W[V, D] computes, for every hidden-state
+ * row h_b, token ids distributed as softmax(W h_b / T_b) without ever writing
+ * logits to memory: logits are formed tile by tile, Gumbel noise is added on
+ * chip and only (max, index) candidates survive (Gumbel-max trick).
+ *
+ * Conventions for every entry point
+ *   - plain C types only; all data pointers are DEVICE pointers owned by the
+ *     caller; nothing is allocated or freed on the sampling path;
+ *   - work is enqueued on the given cudaStream_t (passed as void*), the call
+ *     never synchronises and never throws; the return value is a status code
+ *     (0 = ok), fmms_strerror() names it;
+ *   - `status_dev` (nullable) is an int in device memory that a kernel sets
+ *     to FMMS_ERR_TIMEOUT if one of its bounded waits ran out; the host reads
+ *     it whenever it likes.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative
+ * to the reference project, src/fused_mm_sampling/...).
+ */
+#ifndef FMMS_B200_H_
+#define FMMS_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define FMMS_OK 0
+#define FMMS_ERR_TIMEOUT 1       /* a bounded device-side wait ran out          */
+#define FMMS_ERR_BAD_ARG 2       /* null pointer, non-positive size, bad flags  */
+#define FMMS_ERR_UNSUPPORTED 3   /* shape/alignment the kernels do not handle   */
+#define FMMS_ERR_WORKSPACE 4     /* workspace missing or too small              */
+#define FMMS_ERR_CUDA 5          /* a CUDA runtime/driver call failed           */
+#define FMMS_ERR_ARCH 6          /* device is not compute capability 10.x       */
+
+/* flags of fmms_sample / fmms_sample_tp */
+#define FMMS_FLAG_GREEDY 1         /* argmax of raw logits (core.py GREEDY_SAMPLING, :569-600) */
+#define FMMS_FLAG_EXT_NOISE 2      /* add caller-supplied fp32 noise instead of Philox noise   */
+#define FMMS_FLAG_RETURN_LOGITS 4  /* also store fp32 logits (core.py RETURN_LOGITS, :568-573) */
+#define FMMS_FLAG_FORCE_GEMV 8     /* use the small-batch weight-streaming kernel              */
+#define FMMS_FLAG_FORCE_MMA 16     /* use the tcgen05 tensor-core kernel                       */
+
+/* kernel paths reported by fmms_last_path() */
+#define FMMS_PATH_NONE 0
+#define FMMS_PATH_GEMV 1
+#define FMMS_PATH_MMA 2
+
+/* Library/ABI version (major * 1000 + minor). No reference counterpart. */
+int fmms_version(void);
+
+/* Text for a status code. No reference counterpart (the reference raises
+ * Python exceptions: core.py:235-241). */
+const char* fmms_strerror(int status);
+
+/* Number of SMs of the current device (persistent-grid size). Replaces
+ * num_sms_cached(), core.py:212-214. */
+int fmms_num_sms(int* num_sms);
+
+/* Bytes of scratch the sampling call needs for its per-CTA (max, index)
+ * candidates. Replaces the per-call torch.empty of `maxs` / `maxs_idx`
+ * [num_samples, cdiv(V,128), H] in core.py:262-270 (here: one candidate per
+ * persistent CTA, not per vocabulary tile). */
+int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes);
+
+/*
+ * The fused sampling step on one GPU (or on one vocabulary shard).
+ * Replaces fused_mm_sample_triton(), core.py:224-348 (stage-1 kernel
+ * core.py:480-635 plus stage-2 _local_reduce core.py:359-370).
+ *
+ *   W_bf16        [V_local, D] bf16 row-major, 16-byte aligned, D % 8 == 0
+ *   H_bf16        [B, D] bf16 row-major, 16-byte aligned
+ *   temperature   fp32; temp_stride 0 = one value for all rows (the
+ *                 reference's 0-d tensor, core.py:228,513), 1 = one per row
+ *   S             draws per row (num_samples)
+ *   seed          draw s uses the random stream `seed + s` (core.py:644)
+ *   v_global_offset  global vocabulary id of W's row 0 (tp_rank * vocab_size
+ *                 at core.py:603); also keys the noise so that a sharded run
+ *                 reproduces the unsharded one
+ *   ext_noise     [S, B, noise_ld] fp32, used when FMMS_FLAG_EXT_NOISE;
+ *                 element (s, b, v) is added to logit (b, v) / T_b
+ *   logits_out    [B, V_local] fp32, written when FMMS_FLAG_RETURN_LOGITS
+ *   out_idx       [B, S] int64 global token ids
+ *   out_val       [B, S] fp32 winning perturbed logits (nullable)
+ *   workspace     >= fmms_query_workspace() bytes, 256-byte aligned
+ */
+int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                int V_local, int D, int B, int S, unsigned long long seed,
+                long long v_global_offset, int flags, const float* ext_noise, long long noise_ld,
+                float* logits_out, long long* out_idx, float* out_val, void* workspace,
+                size_t workspace_bytes, int* status_dev, void* stream);
+
+/* Which kernel the last fmms_sample / fmms_sample_tp call of this thread
+ * dispatched to (FMMS_PATH_*). No reference counterpart (the reference has one
+ * kernel and autotunes its tile shape, core.py:442-476). */
+int fmms_last_path(void);
+
+/* Host-only: the launch plan fmms_sample would use on a device with `num_sms`
+ * SMs and `max_smem_bytes` of opt-in shared memory per block; needs no GPU.
+ * plan[0] = FMMS_PATH_*, [1] = persistent CTAs, [2] = vocabulary rows per tile
+ * (row group), [3] = tiles in total, [4] = pipeline stages, [5] = M tiles,
+ * [6] = dynamic shared memory bytes, [7] = candidate rows handed to the
+ * cross-CTA reduction.  Replaces the tile heuristics bsz_h() (core.py:876-881)
+ * and the autotune table (core.py:442-470). */
+int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_smem_bytes, int* plan);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FMMS_B200_H_ */
