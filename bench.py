@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the fused LM-head sampling step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload qwen|llama|gemma] [--batch B]
+    python bench.py --impl reference ...      # the reference's CPU path on the host cores
+
+A step is one sampling call over one batch of hidden states: W[V, d] bf16 is
+streamed once, B rows get one token id each.  Default workload: the Qwen3-8B
+head (V=151936, d=4096, T=0.7, 1 draw per row) at B=64 on one GPU; N > 1 shards
+the vocabulary contiguously over N GPUs (tensor parallel, strong scaling).
+The metric is the latency of a step in microseconds (cold L2: a 256 MB buffer is
+rewritten before every timed call), timed with CUDA events on the launching
+stream, maximum over ranks per step, median over steps.  One JSON line is printed
+by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (V, d, weight std, temperature spec, draws per row)
+    "qwen": dict(V=151936, D=4096, w_std=0.02, temp=("scalar", 0.7), S=1, label="Qwen3-8B head"),
+    "llama": dict(V=128256, D=8192, w_std=0.015, temp=("uniform", 0.5, 1.5), S=1, label="Llama-3-70B head"),
+    "gemma": dict(V=262208, D=5376, w_std=0.02, temp=("scalar", 1.0), S=4, label="Gemma-3-27B head"),
+}
+SWEEP_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+METRIC = "fused_sample_us_per_step"
+
+
+def algorithmic_bytes(V, D, B, S):
+    return 2 * V * D + 2 * B * D + 8 * B * S
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(wl, B, rank, world, device):
+    """Seeded synthetic stand-ins for an LM head, generated on the device."""
+    V, D = wl["V"], wl["D"]
+    g = torch.Generator(device=device).manual_seed(1234)
+    per = V // world
+    v_begin = rank * per
+    v_end = V if rank == world - 1 else v_begin + per
+    # every rank draws the same full stream in chunks and keeps its own rows
+    w = torch.empty((v_end - v_begin, D), dtype=torch.bfloat16, device=device)
+    chunk = 8192
+    for r0 in range(0, V, chunk):
+        r1 = min(V, r0 + chunk)
+        blk = torch.randn((r1 - r0, D), generator=g, device=device, dtype=torch.float32)
+        lo, hi = max(r0, v_begin), min(r1, v_end)
+        if lo < hi:
+            w[lo - v_begin:hi - v_begin] = (blk[lo - r0:hi - r0] * wl["w_std"]).bfloat16()
+    h = torch.randn((B, D), generator=g, device=device, dtype=torch.float32).bfloat16()
+    if wl["temp"][0] == "scalar":
+        t = torch.tensor(wl["temp"][1], dtype=torch.float32, device=device)
+    else:
+        t = torch.rand(B, generator=g, device=device) * (wl["temp"][2] - wl["temp"][1]) + wl["temp"][1]
+    return w, h, t
+
+
+def time_steps(fn, steps, warmup, flush, dist_barrier):
+    """Per-step device times (ms) with a cold L2, plus the wall time of the whole timed region."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    dist_barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    t0 = time.perf_counter()
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        fn()
+        stops[i].record()
+    torch.cuda.synchronize()
+    dist_barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    return [s.elapsed_time(e) for s, e in zip(starts, stops)], wall
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    import flashsampling_b200 as fs
+    from flashsampling_b200 import build
+    from flashsampling_b200.tp_info import TPInfo
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    build.build_library()
+    tp = TPInfo(rank=rank, size=world)
+    wl = WORKLOADS[args.workload]
+    V, D, S = wl["V"], wl["D"], wl["S"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def reduce_max(xs):
+        t = torch.tensor(xs, dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def measure(B, steps, warmup, with_e2e):
+        w, h, t = make_inputs(wl, B, rank, world, device)
+        seed = [0]
+
+        def step():
+            seed[0] += S
+            return fs.fused_mm_sample(w, h, S, t, seed=seed[0], tp=tp)
+
+        step()
+        fs.check_status()
+        path = fs.last_path()
+        with ClockSampler(local_rank) as clk:
+            times, wall = time_steps(step, steps, warmup, flush, barrier)
+        times = reduce_max(times)
+        res = dict(B=B, path=path, times_ms=times, wall_s=wall, clocks=clk.summary())
+        if with_e2e:
+            h_host = h.cpu().pin_memory()
+            t_host = t.cpu().pin_memory()
+            h_dev = torch.empty_like(h)
+            t_dev = torch.empty_like(t)
+
+            def e2e_step():
+                seed[0] += S
+                h_dev.copy_(h_host, non_blocking=True)
+                t_dev.copy_(t_host, non_blocking=True)
+                ids = fs.fused_mm_sample(w, h_dev, S, t_dev, seed=seed[0], tp=tp)
+                return ids.cpu()
+
+            for _ in range(max(3, warmup // 2)):
+                flush.zero_()
+                e2e_step()
+            e2e = []
+            for _ in range(steps):
+                flush.zero_()
+                torch.cuda.synchronize()
+                barrier()
+                t0 = time.perf_counter()
+                e2e_step()
+                e2e.append((time.perf_counter() - t0) * 1e3)
+            res["e2e_ms"] = reduce_max(e2e)
+            res["h2d"] = h_host.numel() * 2 + t_host.numel() * 4
+            res["d2h"] = B * S * 8
+        fs.check_status()
+        del w, h, t
+        return res
+
+    B = args.batch
+    main = measure(B, args.steps, args.warmup, with_e2e=True)
+    sweep = []
+    if args.sweep and world == 1:
+        for b in SWEEP_BATCHES:
+            r = measure(b, max(10, args.steps // 4), max(3, args.warmup // 4), with_e2e=False) if b != B else main
+            us = statistics.median(r["times_ms"]) * 1e3
+            gbs = algorithmic_bytes(V, D, b, S) / (us * 1e-6) / 1e9
+            sweep.append(dict(B=b, us=round(us, 2), path=r["path"], algo_gbs=round(gbs, 1),
+                              frac_of_8tbs=round(gbs / 8000, 4), x_weight_read_at_8tbs=round(us / (2 * V * D / 8e12 * 1e6), 4)))
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    med_us = statistics.median(main["times_ms"]) * 1e3
+    mean_ms = statistics.fmean(main["times_ms"])
+    peak, peak_kind = measured_peaks()
+    v_local = V // world
+    ach = algorithmic_bytes(v_local, D, B, S) / (mean_ms * 1e-3) / 1e9
+    traffic = None
+    tfile = ROOT / "profiles" / "traffic.json"
+    if tfile.exists():
+        traffic = json.loads(tfile.read_text()).get(f"{args.workload}_B{B}_N{world}")
+    line = {
+        "metric": METRIC,
+        "value": round(med_us, 3),
+        "unit": "us",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(mean_ms, 6),
+        "higher_is_better": False,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{wl['label']}: V={V} d={D} bf16, B={B}, {S} draw(s)/row, T={wl['temp']}, "
+                        f"vocabulary sharded over {world} GPU(s)",
+            "batch": B, "vocab": V, "hidden": D, "num_samples": S, "tensor_parallel": world,
+            "kernel": main["path"], "l2": "flushed (256 MB rewrite) before every timed call",
+            "timing": "CUDA events per call on the launch stream, max over ranks, median over steps",
+        },
+        "p10_us": round(sorted(main["times_ms"])[len(main["times_ms"]) // 10] * 1e3, 3),
+        "p90_us": round(sorted(main["times_ms"])[(len(main["times_ms"]) * 9) // 10] * 1e3, 3),
+        "wall_s_timed_region": round(main["wall_s"], 4),
+        "clocks": main["clocks"],
+        "gpu_launches": 2 * args.steps,
+        "e2e": {
+            "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
+            "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"],
+            "note": "pinned host hidden states + temperature -> device, sample, ids -> host; wall clock per step",
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+            "peak_kind": f"of {peak_kind}", "traffic": traffic,
+            "algorithmic_bytes_per_launch": algorithmic_bytes(v_local, D, B, S),
+            "frac_of_8tbs": round(ach / 8000, 4),
+            "note": "duration = mean CUDA-event time of the call (sampling kernel + candidate reduction)",
+        },
+    }
+    if sweep:
+        line["sweep"] = sweep
+    if not args.no_cpu and world == 1:
+        line["cpu_baseline"] = cpu_baseline(wl, B, budget_s=args.cpu_budget)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(wl, B, budget_s=20.0, steps=None, warmup=1):
+    """The reference's torch path (matmul -> /T -> softmax -> multinomial; oracle restatement) on the host
+    cores, on a bounded sample of the workload: the first `rows` vocabulary rows."""
+    from oracle import fmms_oracle as O
+
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    V, D, S = wl["V"], wl["D"], wl["S"]
+    g = torch.Generator().manual_seed(1234)
+    w = (torch.randn(V, D, generator=g) * wl["w_std"]).bfloat16().float()  # upcast once, outside the timed region
+    h = torch.randn(B, D, generator=g).bfloat16().float()
+    t = torch.tensor(wl["temp"][1] if wl["temp"][0] == "scalar" else 1.0)
+    for _ in range(warmup):
+        O.sample(w, h, S, t, seed=0)
+    times = []
+    t_begin = time.perf_counter()
+    n = steps or 1000
+    for i in range(n):
+        t0 = time.perf_counter()
+        O.sample(w, h, S, t, seed=i)
+        times.append(time.perf_counter() - t0)
+        if steps is None and time.perf_counter() - t_begin > budget_s and len(times) >= 3:
+            break
+    return {
+        "value": round(statistics.median(times) * 1e6, 1), "unit": "us", "cores": cores, "kind": "port",
+        "sample": f"{len(times)} full steps of the same workload (B={B}, all {V} rows), fp32 weights upcast from bf16 "
+                  f"outside the timed region, torch {torch.__version__} CPU, {cores} threads",
+    }
+
+
+def run_reference(args):
+    """--impl reference: the reference's own CPU path, timed on the host cores of rank 0."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    steps = max(1, min(args.steps, 20))
+    base = cpu_baseline(wl, args.batch, steps=steps, warmup=max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "us", "n_gpus": args.gpus,
+        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(base["value"] / 1e3, 4),
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{wl['label']}: V={wl['V']} d={wl['D']}, B={args.batch}, {wl['S']} draw(s)/row, "
+                               "reference torch path on the host CPU"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=25)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="qwen", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--sweep", action=argparse.BooleanOptionalAction, default=True)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -135,8 +136,22 @@ static int launch_gemv_nb(DeviceInfo& d, const CUtensorMap& map, SampleParams& p
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
+// Tuning knobs (read once): FMMS_GEMV_STAGES / FMMS_UMMA_STAGES cap the shared-memory ring depth.
+static int env_int(const char* name) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : 0;
+}
+static int gemv_stage_cap() {
+  static const int v = env_int("FMMS_GEMV_STAGES");
+  return v;
+}
+static int umma_stage_cap() {
+  static const int v = env_int("FMMS_UMMA_STAGES");
+  return v;
+}
+
 static int gemv_stages(const DeviceInfo& d, int NB, int D) {
-  int stages = kGemvMaxStages;
+  int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : kGemvMaxStages;
   while (stages >= 3 && gemv_smem_bytes(NB, D, stages) > (size_t)d.max_smem_optin) --stages;
   return stages >= 3 ? stages : 0;
 }
@@ -184,7 +199,7 @@ static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wm, const CUtensorMa
 }
 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
-  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin);
+  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap());
   if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
   CUtensorMap wm, hm;
   int rc = get_tensor_map(W, p.V, p.D, pl.tile_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wm);

@@ -25,7 +25,7 @@ constexpr int kGemvStageBytes = kGemvRows * kGemvCols * 2;        // 16 KiB
 constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer warp
 constexpr int kGemvMaxBatch = 8;
 constexpr int kGemvItemsPerLane = 4;  // (row, b, s) items a lane may own: 4 * NB * S <= 128
-constexpr int kGemvMaxStages = 12;
+constexpr int kGemvMaxStages = 6;  // ~96 KiB in flight per SM: deeper rings measured slower
 
 struct SampleParams {
   const __nv_bfloat16* H;    // [B, D]

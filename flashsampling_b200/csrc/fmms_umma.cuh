@@ -10,7 +10,7 @@
 //
 // Warp roles (384 threads, one CTA per SM, persistent over a contiguous range of
 // vocabulary tiles):
-//   warp 0      TMA producer: W tile + hidden-state tile(s) per pipeline stage
+//   warp 0, 2   TMA producers: W tile / hidden-state tile(s) of each pipeline stage
 //   warp 1      TMEM allocation, then one elected thread issues tcgen05.mma/commit
 //   warps 4-11  epilogue: tcgen05.ld -> scale, noise, running argmax.  TMEM
 //               accumulators are multi-buffered so the epilogue of tile i overlaps
@@ -46,7 +46,7 @@ struct UmmaPlan {
 
 __host__ __device__ inline size_t umma_stage_bytes(int mt) { return (size_t)kUmmaWTileBytes + (size_t)mt * kUmmaHTileBytes; }
 
-__host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem) {
+__host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   pl.nt_cap = pl.mt == 1 ? 256 : 128;
@@ -71,7 +71,7 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem) {
   if (pl.tiles_total < pl.grid) pl.grid = pl.tiles_total;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
   const size_t fixed = 1024 /*barriers etc.*/ + 1024 /*alignment slack*/;
-  int stages = 6;
+  int stages = stages_cap > 1 ? stages_cap : 6;
   while (stages > 2 && stages * umma_stage_bytes(pl.mt) + fixed > (size_t)max_smem) --stages;
   pl.stages = stages;
   pl.smem = stages * umma_stage_bytes(pl.mt) + fixed;
@@ -172,7 +172,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < stages; ++i) {
-      mbar_init(&full_bar[i], 1);
+      mbar_init(&full_bar[i], 2);  // W producer + hidden-state producer
       mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < 4; ++i) {
@@ -201,13 +201,16 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp == 0 || warp == 2) {
+    // ------------------------------ TMA producers -----------------------------
+    // Two threads issue the loads of a stage, warp 0 the W tile and warp 2 the
+    // hidden-state tile(s): a single thread sustains only about three bulk-tensor
+    // operations per microsecond, which would cap the weight stream.
     if (lane == 0) {
-      prefetch_tmap(&w_map);
-      prefetch_tmap(&h_map);
-      const uint64_t pol_w = policy_evict_first(), pol_h = policy_evict_last();
-      const uint32_t tx = (uint32_t)NT * 128u + (uint32_t)MT * (uint32_t)h_rows * 128u;
+      const bool is_w = (warp == 0);
+      prefetch_tmap(is_w ? &w_map : &h_map);
+      const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
+      const uint32_t tx = is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u;
       int it = 0;
       bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t) {
@@ -221,11 +224,14 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           }
           uint8_t* sw = smem + st * stage_bytes;
           mbar_arrive_expect_tx(&full_bar[st], tx);
-          tma_load_2d_hint(sw, &w_map, kb * kUmmaBK, v0, &full_bar[st], pol_w);
+          if (is_w) {
+            tma_load_2d_hint(sw, &w_map, kb * kUmmaBK, v0, &full_bar[st], pol);
+          } else {
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            tma_load_2d_hint(sw + kUmmaWTileBytes + m * kUmmaHTileBytes, &h_map, kb * kUmmaBK, m * 128,
-                             &full_bar[st], pol_h);
+            for (int m = 0; m < MT; ++m)
+              tma_load_2d_hint(sw + kUmmaWTileBytes + m * kUmmaHTileBytes, &h_map, kb * kUmmaBK, m * 128,
+                               &full_bar[st], pol);
+          }
         }
       }
       if (*abort_flag) {

@@ -38,13 +38,13 @@ def _head(V, D, B, w_std=0.05, seed=0):
     return w, h
 
 
-def _check_indices(ids_gpu, logits_cpu, temperature, noise_cpu, label, vals_gpu=None):
+def _check_indices(ids_gpu, logits_cpu, temperature, noise_cpu, label, vals_gpu=None, min_decisive=0.75):
     want, decisive, ymax = O.gumbel_argmax(logits_cpu, temperature, noise_cpu, rel_gap=REL_GAP)
     got = ids_gpu.cpu()
     assert got.shape == want.shape, (label, got.shape, want.shape)
     bad = (got != want) & decisive
     assert not bad.any(), f"{label}: {int(bad.sum())} decisive draws differ, e.g. {bad.nonzero()[:4].tolist()}"
-    assert decisive.float().mean() > 0.9, f"{label}: too few decisive draws to mean anything"
+    assert decisive.float().mean() >= min_decisive, f"{label}: too few decisive draws to mean anything"
     if vals_gpu is not None:
         torch.testing.assert_close(vals_gpu.cpu()[decisive], ymax[decisive], atol=2e-3, rtol=2e-4)
     return int(decisive.sum())
