@@ -13,7 +13,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfmms_b200.so"
 
 # status codes / flags (include/fmms_b200.h)
-OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH = range(7)
+OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(8)
 FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA = 1, 2, 4, 8, 16
 PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
 
@@ -50,6 +50,18 @@ SIGNATURES = {
     ),
     "fmms_last_path": (c_int, []),
     "fmms_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
+    "fmms_static_max_items": (c_int, []),
+    "fmms_sample_static": (
+        c_int,
+        [
+            c_void_p, c_void_p, c_void_p, c_int,  # W, H, temperature, temp_stride
+            c_int, c_int, c_int, c_int,  # V_local, D, B, S
+            c_ulonglong, c_longlong, c_int,  # seed, v_global_offset, flags
+            c_void_p, c_longlong,  # ext_noise, noise_ld
+            c_void_p, c_void_p, c_void_p,  # logits_out, out_idx, out_val
+            c_void_p, c_void_p,  # status_dev, stream
+        ],
+    ),
 }
 
 _lib = None

@@ -213,6 +213,32 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   return pl.grid * 2;
 }
 
+// ---- built-in scratch for callers that cannot allocate --------------------------------
+// Candidate scratch of fmms_sample_static(): room for kMaxParts candidate rows of up to
+// kStaticMaxItems (batch rows x draws) entries, 8 bytes each.  Every GPU on which the
+// library's module is loaded holds these bytes until the process exits.
+constexpr int kStaticMaxItems = 1024;
+constexpr size_t kStaticScratchBytes = (size_t)kMaxParts * kStaticMaxItems * 8 + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address;
+// the address is looked up once per device (with that device current) and cached here.
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+
+static int static_scratch_ptr(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return kErrCuda;
+  if (dev < 0 || dev >= kMaxDevices) return kErrUnsupported;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return kErrCuda;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return kOk;
+}
+
 }  // namespace fmms
 
 using namespace fmms;
@@ -230,6 +256,7 @@ const char* fmms_strerror(int status) {
     case FMMS_ERR_WORKSPACE: return "workspace missing or too small";
     case FMMS_ERR_CUDA: return "CUDA call failed";
     case FMMS_ERR_ARCH: return "device is not compute capability 10.x (sm_100a)";
+    case FMMS_ERR_TOO_LARGE: return "batch rows x draws exceeds the built-in scratch (fmms_static_max_items)";
     default: return "unknown status";
   }
 }
@@ -359,6 +386,24 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.cand_val, p.cand_idx, parts, B, S,
                                                                  v_global_offset, out_idx, out_val);
   return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+int fmms_static_max_items(void) { return kStaticMaxItems; }
+
+int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                       int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                       int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                       long long* out_idx, float* out_val, int* status_dev, void* stream) {
+  if (B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
+  if ((long long)B * (long long)S > kStaticMaxItems) return FMMS_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);  // first call on a device: symbol-address look-up
+  if (rc != kOk) return rc;
+  // Nothing in the scratch has to start at zero: the sampling kernels write every candidate
+  // entry that the reduction reads, so the previous call's contents are simply overwritten.
+  return fmms_sample(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
+                     ext_noise, noise_ld, logits_out, out_idx, out_val, scratch, kStaticScratchBytes, status_dev,
+                     stream);
 }
 
 }  // extern "C"

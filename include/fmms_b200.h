@@ -36,6 +36,7 @@ extern "C" {
 #define FMMS_ERR_WORKSPACE 4     /* workspace missing or too small              */
 #define FMMS_ERR_CUDA 5          /* a CUDA runtime/driver call failed           */
 #define FMMS_ERR_ARCH 6          /* device is not compute capability 10.x       */
+#define FMMS_ERR_TOO_LARGE 7     /* B * S exceeds the built-in scratch          */
 
 /* flags of fmms_sample / fmms_sample_tp */
 #define FMMS_FLAG_GREEDY 1         /* argmax of raw logits (core.py GREEDY_SAMPLING, :569-600) */
@@ -106,6 +107,38 @@ int fmms_last_path(void);
  * cross-CTA reduction.  Replaces the tile heuristics bsz_h() (core.py:876-881)
  * and the autotune table (core.py:442-470). */
 int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_smem_bytes, int* plan);
+
+/*
+ * fmms_sample() for callers that cannot hand over a workspace because they cannot
+ * allocate device memory at all: a plugin inside a serving process that reserved the
+ * whole GPU for its own pool at start-up, a plain C host with no allocator of its own,
+ * or a decode loop in which cudaMalloc (and the device-wide synchronisation it implies)
+ * is forbidden once serving has begun.  It has no counterpart in the reference, which
+ * allocates its candidate buffers with torch.empty on every call.
+ *
+ * Same arguments and results as fmms_sample() minus `workspace`: the candidate scratch
+ * is an array built into the library's device image (about 2.5 MiB, resident on every
+ * GPU that loads the library until the process exits).  The call itself allocates
+ * nothing, on the device or through any library.
+ *
+ *   - limit: B * S <= fmms_static_max_items() (1024); larger problems return
+ *     FMMS_ERR_TOO_LARGE and launch nothing;
+ *   - the first call on each device looks the array's device address up (with that
+ *     device current) and caches it; make that first call before any stream capture
+ *     is begun on the device;
+ *   - all calls on a device share the one array: two calls whose kernels overlap on the
+ *     GPU (different streams without an ordering between them) race on it.  Calls on
+ *     one stream, or ordered by events, are safe.  The array keeps the last call's
+ *     candidates; nothing in it needs clearing between calls.
+ */
+int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                       int V_local, int D, int B, int S, unsigned long long seed,
+                       long long v_global_offset, int flags, const float* ext_noise, long long noise_ld,
+                       float* logits_out, long long* out_idx, float* out_val, int* status_dev,
+                       void* stream);
+
+/* Largest B * S that fmms_sample_static() accepts. No reference counterpart. */
+int fmms_static_max_items(void);
 
 #ifdef __cplusplus
 }
