@@ -50,6 +50,16 @@ SIGNATURES = {
     ),
     "fmms_last_path": (c_int, []),
     "fmms_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
+    "fmms_tp_buffer_bytes": (c_int, [c_int, c_int, ctypes.POINTER(c_size_t)]),
+    "fmms_tp_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
+    "fmms_tp_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "fmms_tp_close": (c_int, [c_void_p]),
+    "fmms_tp_free": (c_int, [c_void_p]),
+    "fmms_tp_exchange": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.c_uint,
+         c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "fmms_static_max_items": (c_int, []),
     "fmms_sample_static": (
         c_int,

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -12,6 +13,7 @@
 #include "fmms_common.cuh"
 #include "fmms_gemv.cuh"
 #include "fmms_umma.cuh"
+#include "fmms_tp.cuh"
 
 namespace fmms {
 
@@ -385,6 +387,70 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   const int n = B * S;
   reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.cand_val, p.cand_idx, parts, B, S,
                                                                  v_global_offset, out_idx, out_val);
+  return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+// ---- tensor-parallel exchange -----------------------------------------------------------
+int fmms_tp_buffer_bytes(int world, int max_items, size_t* bytes) {
+  if (!bytes || world < 1 || world > kTpMaxWorld || max_items < 1) return FMMS_ERR_BAD_ARG;
+  *bytes = tp_buffer_bytes(world, max_items);
+  return FMMS_OK;
+}
+
+int fmms_tp_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_64) {
+  if (!dev_ptr || !ipc_handle_64 || bytes == 0) return FMMS_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return FMMS_ERR_CUDA;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess) return FMMS_ERR_CUDA;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+    cudaFree(p);
+    return FMMS_ERR_CUDA;
+  }
+  memcpy(ipc_handle_64, &h, 64);
+  *dev_ptr = p;
+  return FMMS_OK;
+}
+
+int fmms_tp_open(const void* ipc_handle_64, void** peer_ptr) {
+  if (!ipc_handle_64 || !peer_ptr) return FMMS_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle_64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return FMMS_ERR_CUDA;
+  *peer_ptr = p;
+  return FMMS_OK;
+}
+
+int fmms_tp_close(void* peer_ptr) {
+  if (!peer_ptr) return FMMS_ERR_BAD_ARG;
+  return cudaIpcCloseMemHandle(peer_ptr) == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+int fmms_tp_free(void* dev_ptr) {
+  if (!dev_ptr) return FMMS_ERR_BAD_ARG;
+  return cudaFree(dev_ptr) == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_items, int max_items, int rank,
+                     int world, void* const* peer_buffers, unsigned int epoch,
+                     unsigned long long wait_limit_ns, long long* out_idx, float* out_val, int* status_dev,
+                     void* stream) {
+  if (!local_idx || !local_val || !out_idx || !peer_buffers) return FMMS_ERR_BAD_ARG;
+  if (world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return FMMS_ERR_BAD_ARG;
+  if (n_items < 1 || n_items > max_items) return FMMS_ERR_BAD_ARG;
+  TpPeers peers{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_buffers[r]) return FMMS_ERR_BAD_ARG;
+    peers.slots[r] = reinterpret_cast<TpRecord*>(peer_buffers[r]);
+    peers.flags[r] = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(peer_buffers[r]) +
+                                                     (size_t)2 * world * max_items * sizeof(TpRecord));
+  }
+  const int threads = n_items >= 1024 ? 1024 : ((n_items + 31) / 32 * 32 < 32 ? 32 : (n_items + 31) / 32 * 32);
+  tp_exchange_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      local_idx, local_val, n_items, max_items, rank, world, peers, epoch,
+      wait_limit_ns ? wait_limit_ns : kWaitLimitNs, out_idx, out_val, status_dev);
   return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
 }
 

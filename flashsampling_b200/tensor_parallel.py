@@ -1,0 +1,165 @@
+"""Vocabulary-sharded tensor parallelism: the cross-rank step of the sampling path.
+
+Replaces the reference's ``tensor_parallel_reduce.py`` (symmetric-memory workspace with
+``world * num_samples * tiles * B`` candidates per rank, fan-out stores inside the Triton
+kernel, host-launched barrier, inductor reduce).  Here every rank first reduces to ONE
+``(value, id)`` per row and draw on its own GPU; the exchange then moves 16 bytes per row
+and peer.
+
+Two interchangeable exchanges:
+
+* ``PeerExchange`` (default on GPUs): one small CUDA kernel per step writes the records
+  into every rank's buffer over NVLink peer memory, signals epoch flags and waits
+  (bounded) for the peers - no NCCL, no host barrier.  Buffers are plain ``cudaMalloc``
+  memory shared through CUDA IPC handles that travel once through ``torch.distributed``.
+* ``CollectiveExchange``: ``all_gather`` of values and ids through ``torch.distributed``
+  (NCCL on GPUs - the measured baseline - or gloo on CPU tensors for tests) followed by
+  ``reduce_gathered``.
+
+Both give every rank the same result, equal to the unsharded draw because the kernels' noise
+is keyed by global vocabulary ids.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .tp_info import TPInfo
+
+MAX_ITEMS = 32768  # rows x draws per exchange step; larger calls are exchanged in chunks
+
+
+def reduce_gathered(vals: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Winner over the leading (rank) axis of gathered ``[world, ...]`` values and ids.
+
+    Larger value wins; equal values resolve to the smaller id, the same order the kernels
+    use, so the result does not depend on the sharding.
+    """
+    best = vals.max(dim=0).values
+    is_best = vals == best.unsqueeze(0)
+    big = torch.iinfo(torch.int64).max
+    win_id = torch.where(is_best, ids, torch.full_like(ids, big)).min(dim=0).values
+    return win_id, best
+
+
+class CollectiveExchange:
+    """all_gather through torch.distributed (NCCL baseline on GPUs, gloo on CPU)."""
+
+    def __init__(self, tp: TPInfo, device: torch.device, group=None):
+        self.tp, self.device, self.group = tp, device, group
+
+    def vocab_offset(self, v_local: int) -> int:
+        return self.tp.rank * v_local
+
+    def reduce(self, ids: torch.Tensor, vals: torch.Tensor):
+        world = self.tp.size
+        n = vals.numel()
+        g_vals = torch.empty(world * n, dtype=vals.dtype, device=vals.device)
+        g_ids = torch.empty(world * n, dtype=ids.dtype, device=ids.device)
+        dist.all_gather_into_tensor(g_vals, vals.reshape(-1).contiguous(), group=self.group)
+        dist.all_gather_into_tensor(g_ids, ids.reshape(-1).contiguous(), group=self.group)
+        win, best = reduce_gathered(g_vals.view(world, n), g_ids.view(world, n))
+        return win.view(ids.shape), best.view(vals.shape)
+
+
+class PeerExchange:
+    """Exchange kernel over NVLink peer memory (CUDA IPC buffers, epoch flags)."""
+
+    def __init__(self, tp: TPInfo, device: torch.device, max_items: int = MAX_ITEMS):
+        if device.type != "cuda":
+            raise RuntimeError("PeerExchange needs CUDA devices")
+        if tp.size > 8:
+            raise ValueError("at most 8 ranks (one NVLink domain)")
+        self.tp, self.device, self.max_items = tp, device, max_items
+        self.lib = _lib.load()
+        self.epoch = 0
+        n = ctypes.c_size_t(0)
+        _lib.check(self.lib.fmms_tp_buffer_bytes(tp.size, max_items, ctypes.byref(n)), "fmms_tp_buffer_bytes")
+        self.nbytes = int(n.value)
+        with torch.cuda.device(device):
+            own = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(self.lib.fmms_tp_alloc(self.nbytes, ctypes.byref(own), handle), "fmms_tp_alloc")
+            self.own = own
+            handles: list = [None] * tp.size
+            dist.all_gather_object(handles, bytes(handle.raw))
+            ptrs = (ctypes.c_void_p * tp.size)()
+            self._opened = []
+            for r, h in enumerate(handles):
+                if r == tp.rank:
+                    ptrs[r] = own.value
+                else:
+                    peer = ctypes.c_void_p()
+                    _lib.check(self.lib.fmms_tp_open(ctypes.create_string_buffer(h, 64), ctypes.byref(peer)),
+                               f"fmms_tp_open(rank {r})")
+                    ptrs[r] = peer.value
+                    self._opened.append(peer)
+            self.ptrs = ptrs
+        dist.barrier()  # every rank has mapped every buffer before the first step
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def vocab_offset(self, v_local: int) -> int:
+        return self.tp.rank * v_local
+
+    def reduce(self, ids: torch.Tensor, vals: torch.Tensor):
+        flat_ids, flat_vals = ids.reshape(-1), vals.reshape(-1)
+        out_ids, out_vals = torch.empty_like(flat_ids), torch.empty_like(flat_vals)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        n = flat_ids.numel()
+        with torch.cuda.device(self.device):
+            for lo in range(0, n, self.max_items):
+                cnt = min(self.max_items, n - lo)
+                self.epoch += 1
+                rc = self.lib.fmms_tp_exchange(
+                    flat_ids[lo:].data_ptr(), flat_vals[lo:].data_ptr(), cnt, self.max_items, self.tp.rank,
+                    self.tp.size, self.ptrs, self.epoch, 0, out_ids[lo:].data_ptr(), out_vals[lo:].data_ptr(),
+                    self.status.data_ptr(), stream,
+                )
+                _lib.check(rc, "fmms_tp_exchange")
+        return out_ids.reshape(ids.shape), out_vals.reshape(vals.shape)
+
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise _lib.FmmsError(code, "fmms_tp_exchange (device status word)")
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            self.lib.fmms_tp_close(p)
+        self._opened = []
+        if self.own:
+            self.lib.fmms_tp_free(self.own)
+            self.own = None
+
+
+_exchanges: dict = {}
+
+
+def exchange_mode() -> str:
+    """"p2p" (default) or "nccl": set FMMS_TP_EXCHANGE to choose."""
+    return os.environ.get("FMMS_TP_EXCHANGE", "p2p")
+
+
+def get_exchange(tp: TPInfo, device: torch.device):
+    """The exchange of this process for (tp, device); created collectively on first use."""
+    mode = exchange_mode() if device.type == "cuda" else "nccl"
+    key = (tp.rank, tp.size, str(device), mode)
+    ex = _exchanges.get(key)
+    if ex is None:
+        ex = PeerExchange(tp, device) if mode == "p2p" else CollectiveExchange(tp, device)
+        _exchanges[key] = ex
+    return ex
+
+
+def close_exchanges() -> None:
+    for ex in _exchanges.values():
+        if isinstance(ex, PeerExchange):
+            ex.close()
+    _exchanges.clear()

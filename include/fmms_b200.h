@@ -108,6 +108,41 @@ int fmms_last_path(void);
  * and the autotune table (core.py:442-470). */
 int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_smem_bytes, int* plan);
 
+/* ---- tensor parallelism: vocabulary shards on the GPUs of one NVLink domain ------------
+ *
+ * Each rank samples its own block with fmms_sample() (v_global_offset = first global row of
+ * the block, out_val requested) and then calls fmms_tp_exchange(): every rank writes its
+ * per-row (value, id) winners into every rank's symmetric buffer with plain peer stores,
+ * signals an epoch flag, waits (bounded) for the other ranks' flags and keeps the largest
+ * value per row.  All ranks end with the same ids.  This replaces the symmetric-memory
+ * fan-out of per-tile candidates plus host-launched barrier and reduce of the reference:
+ * allocate_symm_mem_outputs / tp_post_kernel_reduce (tensor_parallel_reduce.py:21-85) and
+ * the in-kernel peer stores (core.py:614-632).
+ */
+
+/* Size of one rank's symmetric buffer for `world` ranks and up to `max_items` (B * S)
+ * items per step. */
+int fmms_tp_buffer_bytes(int world, int max_items, size_t* bytes);
+
+/* Set-up, not on the sampling path: allocate (and zero) this rank's buffer and produce the
+ * 64-byte CUDA IPC handle that the other ranks open.  Replaces
+ * symm_mem.get_symm_mem_workspace (tensor_parallel_reduce.py:45-48). */
+int fmms_tp_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_64);
+int fmms_tp_open(const void* ipc_handle_64, void** peer_ptr);
+int fmms_tp_close(void* peer_ptr);
+int fmms_tp_free(void* dev_ptr);
+
+/* The exchange step (one small kernel).  `peer_buffers[world]` are the device pointers of
+ * every rank's buffer as seen from this process (own buffer at index `rank`); `epoch` must
+ * be the same on all ranks and grow by one per step, starting at 1; `wait_limit_ns` bounds
+ * the flag wait (0 = 2 s), after which FMMS_ERR_TIMEOUT is written to `status_dev` and the
+ * ids are set to -1.  Replaces symm_mem_hdl.barrier() + _local_reduce over world * tiles
+ * (tensor_parallel_reduce.py:77-84). */
+int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_items, int max_items,
+                     int rank, int world, void* const* peer_buffers, unsigned int epoch,
+                     unsigned long long wait_limit_ns, long long* out_idx, float* out_val,
+                     int* status_dev, void* stream);
+
 /*
  * fmms_sample() for callers that cannot hand over a workspace because they cannot
  * allocate device memory at all: a plugin inside a serving process that reserved the

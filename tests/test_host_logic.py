@@ -1,0 +1,106 @@
+"""CPU tests: the C ABI loads and exports every declared symbol, host-side planning and argument
+checks (no compute call needs a GPU here), and the tensor-parallel host logic."""
+
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from flashsampling_b200 import _lib
+
+    header = (ROOT / "include" / "fmms_b200.h").read_text()
+    declared = set(re.findall(r"\b(fmms_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found in the header"
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/fmms_b200.h but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    assert lib.fmms_version() >= 1000
+    assert _lib.strerror(0) == "ok" and "timed out" in _lib.strerror(1)
+
+
+def test_workspace_query_and_bad_arguments(lib):
+    from flashsampling_b200 import _lib
+
+    assert _lib.query_workspace(151936, 4096, 64, 1) >= 296 * 64 * 8
+    assert _lib.query_workspace(100, 16, 2, 10_000) >= 296 * 2 * 10_000 * 8
+    import ctypes
+
+    n = ctypes.c_size_t()
+    assert lib.fmms_query_workspace(0, 16, 1, 1, ctypes.byref(n)) == _lib.ERR_BAD_ARG
+    # argument checks come before any CUDA call, so they are testable without a GPU
+    rc = lib.fmms_sample(None, None, None, 0, 10, 8, 1, 1, 0, 0, 0, None, 0, None, None, None, None, 0, None, None)
+    assert rc == _lib.ERR_BAD_ARG
+    rc = lib.fmms_sample_static(None, None, None, 0, 10, 8, 64, 64, 0, 0, 0, None, 0, None, None, None, None, None)
+    assert rc == _lib.ERR_TOO_LARGE
+
+
+@pytest.mark.parametrize("V,D", [(151936, 4096), (128256, 8192), (262208, 5376), (16032, 8192), (32776, 5376), (100, 16), (513, 64)])
+@pytest.mark.parametrize("B", [1, 4, 8, 16, 64, 128, 129, 256])
+def test_launch_plan_covers_the_vocabulary(lib, V, D, B):
+    from flashsampling_b200 import _lib
+
+    for flags in (0, _lib.FLAG_FORCE_MMA):
+        pl = _lib.plan(V, D, B, 1, flags=flags)
+        assert pl["grid"] >= 1 and pl["grid"] <= 148
+        assert pl["tile_rows"] * pl["tiles_total"] >= V > pl["tile_rows"] * (pl["tiles_total"] - 1)
+        assert pl["smem_bytes"] <= 232448
+        assert pl["candidate_rows"] <= 320
+        if pl["path"] == _lib.PATH_MMA:
+            assert pl["tile_rows"] % 16 == 0 and 16 <= pl["tile_rows"] <= (256 if B <= 128 else 128)
+            assert pl["m_tiles"] == (2 if B > 128 else 1)
+            busiest = -(-pl["tiles_total"] // pl["grid"]) * pl["tile_rows"]
+            if V >= 148 * 128:
+                assert busiest <= 1.15 * V / pl["grid"] + 16, "tile choice leaves the busiest CTA too much work"
+        else:
+            assert B <= 8 and pl["tile_rows"] == 32 and pl["stages"] >= 3
+
+
+def test_plan_dispatch_rules(lib):
+    from flashsampling_b200 import _lib
+
+    assert _lib.plan(151936, 4096, 1, 1)["path"] == _lib.PATH_GEMV
+    assert _lib.plan(151936, 4096, 64, 1)["path"] == _lib.PATH_MMA
+    assert _lib.plan(512, 16, 1, 10_000)["path"] == _lib.PATH_MMA  # too many draws for register candidates
+    assert _lib.plan(151936, 4096, 8, 4, flags=_lib.FLAG_FORCE_GEMV)["path"] == _lib.PATH_GEMV
+    with pytest.raises(_lib.FmmsError):
+        _lib.plan(151936, 4096, 9, 1, flags=_lib.FLAG_FORCE_GEMV)
+    with pytest.raises(_lib.FmmsError):
+        _lib.plan(1000, 12, 1, 1)  # D not a multiple of 8 (16-byte rows)
+
+
+def test_python_entry_point_rejects_cpu_tensors_and_bad_shapes():
+    import flashsampling_b200 as fs
+
+    w = torch.zeros(64, 16, dtype=torch.bfloat16)
+    h = torch.zeros(2, 16, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fs.fused_mm_sample_triton(w, h, 1, torch.tensor(1.0), seed=0)
+    with pytest.raises(NotImplementedError):
+        fs.get_sampler("flashinfer:sampling_from_logits", w)
+    assert {"fused-triton", "fused-b200"} <= set(fs.PROVIDERS)
+    s = fs.get_sampler("fused-triton", w)
+    assert s.prepare() is s
+
+
+def test_reduce_gathered_prefers_value_then_lowest_id():
+    from flashsampling_b200.tensor_parallel import reduce_gathered
+
+    vals = torch.tensor([[1.0, 5.0, 2.0], [3.0, 5.0, -1.0], [3.0, 4.0, 2.0]])
+    ids = torch.tensor([[10, 99, 7], [20, 50, 8], [15, 1, 3]])
+    win, best = reduce_gathered(vals, ids)
+    assert win.tolist() == [15, 50, 3] and best.tolist() == [3.0, 5.0, 2.0]
+
+
+def test_tp_buffer_size(lib):
+    import ctypes
+
+    n = ctypes.c_size_t()
+    assert lib.fmms_tp_buffer_bytes(8, 1024, ctypes.byref(n)) == 0
+    assert n.value == 2 * 8 * 1024 * 16 + 8 * 128
+    assert lib.fmms_tp_buffer_bytes(9, 1024, ctypes.byref(n)) != 0

@@ -1,0 +1,53 @@
+"""World-size-2 (and 4) tensor-parallel logic on CPU ranks over gloo: every rank computes the oracle's
+winners on its own vocabulary block, the collective exchange merges them, and the result must equal
+the unsharded oracle draw."""
+
+import numpy as np
+import pytest
+import torch
+
+
+def _tp_worker(world, seed):
+    import torch.distributed as dist
+
+    from flashsampling_b200.tensor_parallel import CollectiveExchange
+    from flashsampling_b200.testing import gaussian_head, shard_weights
+    from flashsampling_b200.tp_info import TPInfo
+    from oracle import fmms_oracle as O
+
+    tp = TPInfo.from_world()
+    assert tp.size == world
+    V, D, B, S = 1024, 64, 5, 3
+    w, h = gaussian_head(V, D, B, 0.2, seed=seed)
+    noise = O.kernel_noise(seed, S, B, 0, V)  # keyed by global ids: identical on every rank
+    full_idx, decisive, full_val = O.gumbel_argmax(O.logits_fp32(w, h), 0.9, noise)
+    lo, hi = tp.shard_rows(V)
+    w_local = shard_weights(w, tp)
+    assert w_local.shape[0] == hi - lo
+    loc_idx, _, loc_val = O.gumbel_argmax(O.logits_fp32(w_local, h), 0.9, noise[:, :, lo:hi])
+    ex = CollectiveExchange(tp, torch.device("cpu"))
+    assert ex.vocab_offset(hi - lo) == lo
+    ids, vals = ex.reduce(loc_idx + lo, loc_val)
+    assert torch.equal(ids, full_idx), (tp.rank, ids, full_idx)
+    assert torch.equal(vals, full_val)
+    # every rank holds the same answer
+    gathered = [torch.empty_like(ids) for _ in range(world)]
+    dist.all_gather(gathered, ids)
+    assert all(torch.equal(g, ids) for g in gathered)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_vocab_sharded_draw_equals_unsharded_draw_gloo(world):
+    from flashsampling_b200.tp_info import run_maybe_distributed
+
+    run_maybe_distributed(_tp_worker, world, world, 17)
+
+
+def test_shard_rows_cover_vocab_without_overlap():
+    from flashsampling_b200.tp_info import TPInfo
+
+    for V in (100, 151936, 128256, 262208, 1001):
+        for size in (1, 2, 4, 8):
+            spans = [TPInfo(r, size).shard_rows(V) for r in range(size)]
+            assert spans[0][0] == 0 and spans[-1][1] == V
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
