@@ -39,7 +39,8 @@ def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tenso
     key = (device.index, stream_id)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        # zeroed once: the kernels keep the head of the workspace (packed winners, CTA counter) at zero
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -66,6 +67,9 @@ def check_status(device: torch.device | None = None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
+            for key, ws in _workspaces.items():
+                if key[0] == idx:
+                    ws.zero_()  # an aborted kernel may have left candidates behind
             raise _lib.FmmsError(code, "fused_mm_sample (device status word)")
 
 
@@ -87,6 +91,7 @@ def fused_mm_sample(
     noise: torch.Tensor | None = None,  # [num_samples, B, V_local] or [B, V_local] fp32: replaces the generator
     kernel: str | None = None,  # None = automatic, "gemv" or "mma" forces a kernel
     return_values: bool = False,
+    two_stage: bool = False,  # decode the winners in a second kernel instead of the last CTA
 ):
     """Sample ``num_samples`` token ids per hidden-state row from softmax(W h / T).
 
@@ -159,6 +164,8 @@ def fused_mm_sample(
         flags |= _lib.FLAG_FORCE_MMA
     elif kernel is not None:
         raise ValueError('kernel must be None, "gemv" or "mma"')
+    if two_stage:
+        flags |= _lib.FLAG_TWO_STAGE
 
     v_begin = 0
     if tp.size > 1:

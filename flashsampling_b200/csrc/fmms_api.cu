@@ -124,6 +124,15 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, int b
   return kOk;
 }
 
+// Workspace layout, a function of the workspace SIZE only (so calls of different shapes that
+// share one workspace agree on it): [ticket: 256 B][keys: cap u64][running candidates:
+// kMaxParts * cap * (f32 + i32)], cap = the number of (row, draw) items the size can hold.
+// Ticket and keys must be zero when a call starts; every call leaves them zero again.
+static size_t workspace_bytes_for(int B, int S) {
+  return 256 + (size_t)B * (size_t)S * 8 * (1 + (size_t)kMaxParts);
+}
+static size_t workspace_item_capacity(size_t bytes) { return (bytes - 256) / (8 * (1 + (size_t)kMaxParts)); }
+
 // ---- GEMV launch ----------------------------------------------------------------
 template <int NB>
 static int launch_gemv_nb(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
@@ -220,7 +229,7 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
 // kStaticMaxItems (batch rows x draws) entries, 8 bytes each.  Every GPU on which the
 // library's module is loaded holds these bytes until the process exits.
 constexpr int kStaticMaxItems = 1024;
-constexpr size_t kStaticScratchBytes = (size_t)kMaxParts * kStaticMaxItems * 8 + 256;
+constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxItems * 8 * (1 + (size_t)kMaxParts);
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address;
@@ -274,7 +283,7 @@ int fmms_num_sms(int* num_sms) {
 
 int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes) {
   if (!bytes || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
-  *bytes = (size_t)kMaxParts * (size_t)B * (size_t)S * 8 + 256;
+  *bytes = workspace_bytes_for(B, S);
   return FMMS_OK;
 }
 
@@ -359,8 +368,14 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   p.ext_noise = ext_noise;
   p.noise_ld = noise_ld;
   p.logits_out = logits_out;
-  p.cand_val = reinterpret_cast<float*>(workspace);
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  const size_t cap = workspace_item_capacity(workspace_bytes);
+  p.ticket = reinterpret_cast<unsigned int*>(ws);
+  p.keys = reinterpret_cast<unsigned long long*>(ws + 256);
+  p.cand_val = reinterpret_cast<float*>(ws + 256 + cap * 8);
   p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
+  p.out_idx = out_idx;
+  p.out_val = out_val;
   p.status_dev = status_dev;
 
   const bool can_gemv = gemv_eligible(*d, D, B, S);
@@ -384,10 +399,12 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   }
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
 
-  const int n = B * S;
-  reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.cand_val, p.cand_idx, parts, B, S,
-                                                                 v_global_offset, out_idx, out_val);
-  return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+  if (flags & FMMS_FLAG_TWO_STAGE) {
+    const int n = B * S;
+    reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.keys, B, S, v_global_offset, out_idx, out_val);
+    return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+  }
+  return FMMS_OK;
 }
 
 // ---- tensor-parallel exchange -----------------------------------------------------------
@@ -465,8 +482,10 @@ int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temp
   void* scratch = nullptr;
   const int rc = static_scratch_ptr(&scratch);  // first call on a device: symbol-address look-up
   if (rc != kOk) return rc;
-  // Nothing in the scratch has to start at zero: the sampling kernels write every candidate
-  // entry that the reduction reads, so the previous call's contents are simply overwritten.
+  // The head of the scratch (packed winners and the CTA counter) has to be zero when a call
+  // starts: the array is zero when the module is loaded, and every call's last CTA puts the
+  // zeros back after decoding, so nothing is cleared here.  The running candidates behind it
+  // are initialised by the kernel that uses them.
   return fmms_sample(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
                      ext_noise, noise_ld, logits_out, out_idx, out_val, scratch, kStaticScratchBytes, status_dev,
                      stream);

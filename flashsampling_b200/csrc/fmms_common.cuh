@@ -15,7 +15,7 @@ namespace fmms {
 constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kErrWorkspace = 4,
               kErrCuda = 5, kErrArch = 6;
 constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
-              kFlagForceMma = 16;
+              kFlagForceMma = 16, kFlagTwoStage = 32;
 
 constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"
 
@@ -92,6 +92,27 @@ __device__ __forceinline__ void warp_cand_allreduce(float& v, int& i) {
     const int i2 = __shfl_xor_sync(0xffffffffu, i, off);
     cand_merge(v, i, v2, i2);
   }
+}
+
+// A candidate packed into 64 bits so that one atomicMax keeps the winner: the high word is
+// the value mapped to an order-preserving unsigned integer, the low word the complemented
+// index (equal values resolve to the lower index).  Zero means "no candidate".
+__device__ __forceinline__ unsigned long long cand_key(float v, int idx) {
+  uint32_t b = __float_as_uint(v);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return ((unsigned long long)b << 32) | (unsigned long long)(~(uint32_t)idx);
+}
+
+__device__ __forceinline__ void cand_key_decode(unsigned long long k, float& v, int& idx) {
+  if (k == 0ull) {
+    v = -INFINITY;
+    idx = 0;
+    return;
+  }
+  uint32_t b = (uint32_t)(k >> 32);
+  b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
+  v = __uint_as_float(b);
+  idx = (int)(~(uint32_t)k);
 }
 
 // ------------------------------------------------------------------------------------

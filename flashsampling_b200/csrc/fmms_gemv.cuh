@@ -38,13 +38,42 @@ struct SampleParams {
   const float* ext_noise;    // [S, B, noise_ld]
   long long noise_ld;
   float* logits_out;         // [B, V]
-  float* cand_val;           // [gridDim.x, S * B]
-  int* cand_idx;             // [gridDim.x, S * B]
+  unsigned long long* keys;  // [S * B] packed winners, zero on entry and on exit (atomicMax target)
+  unsigned int* ticket;      // CTAs-done counter, zero on entry and on exit
+  float* cand_val;           // [2 * gridDim.x, S * B] running per-CTA candidates (tensor-core path, S > 1)
+  int* cand_idx;
+  long long* out_idx;        // [B, S]
+  float* out_val;            // [B, S] or null
   int* status_dev;
   int stages;                // shared-memory ring depth
   int tile_rows;             // tensor-core path: vocabulary rows per tile
   int tiles_per_cta;         // tensor-core path
 };
+
+// Last step of a sampling kernel, run by `nthreads` threads of every CTA after their packed
+// candidates went into p.keys with atomicMax: the CTA that takes the last ticket decodes the
+// winners into the output and leaves keys and ticket zero for the next launch.
+template <class SyncFn>
+__device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, int nthreads, SyncFn sync,
+                                              volatile int* is_last) {
+  __threadfence();
+  sync();
+  if (tid == 0) *is_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  sync();
+  if (!*is_last) return;
+  __threadfence();
+  const int n = p.B * p.S;
+  for (int item = tid; item < n; item += nthreads) {
+    const unsigned long long k = atomicExch(&p.keys[item], 0ull);
+    float v;
+    int idx;
+    cand_key_decode(k, v, idx);
+    const int s = item / p.B, b = item - s * p.B;
+    p.out_idx[(size_t)b * p.S + s] = p.v_offset + idx;
+    if (p.out_val) p.out_val[(size_t)b * p.S + s] = v;
+  }
+  if (tid == 0) *p.ticket = 0u;
+}
 
 __host__ __device__ inline int gemv_dpad(int D) { return (D + kGemvCols - 1) / kGemvCols * kGemvCols; }
 
@@ -266,32 +295,32 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
 #pragma unroll
     for (int w = 1; w < kGemvConsumerWarps; ++w) cand_merge(bv, bi, red_val[w * 32 + tid], red_idx[w * 32 + tid]);
     const int b = tid % NB, s = tid / NB;
-    if (b < p.B) {
-      const size_t o = (size_t)blockIdx.x * (p.S * p.B) + (size_t)s * p.B + b;
-      p.cand_val[o] = bv;
-      p.cand_idx[o] = bi;
-    }
+    if (b < p.B && bi != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(bv, bi));
+  }
+  if (!(p.flags & kFlagTwoStage)) {
+    volatile int* is_last = abort_flag + 1;
+    finish_sample(
+        p, tid, kGemvConsumerWarps * 32,
+        [] { asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory"); }, is_last);
   }
 }
 
 // ---------------------------------------------------------------------------------
-// Cross-CTA reduction: one thread per (b, s) scans the per-CTA candidates.
+// Stand-alone second stage (FMMS_FLAG_TWO_STAGE): the sampling kernel only merges its
+// candidates into p.keys; this kernel decodes the winners and clears the keys.
 // ---------------------------------------------------------------------------------
-__global__ void reduce_candidates_kernel(const float* __restrict__ cand_val,
-                                         const int* __restrict__ cand_idx, int parts, int B, int S,
-                                         long long v_offset, long long* __restrict__ out_idx,
-                                         float* __restrict__ out_val) {
+__global__ void reduce_candidates_kernel(unsigned long long* __restrict__ keys, int B, int S, long long v_offset,
+                                         long long* __restrict__ out_idx, float* __restrict__ out_val) {
   const int item = blockIdx.x * blockDim.x + threadIdx.x;  // s * B + b
-  const int n = B * S;
-  if (item >= n) return;
-  float bv = -INFINITY;
-  int bi = kIdxNone;
-  for (int pidx = 0; pidx < parts; ++pidx) {
-    cand_merge(bv, bi, cand_val[(size_t)pidx * n + item], cand_idx[(size_t)pidx * n + item]);
-  }
+  if (item >= B * S) return;
+  const unsigned long long k = keys[item];
+  keys[item] = 0ull;
+  float v;
+  int idx;
+  cand_key_decode(k, v, idx);
   const int s = item / B, b = item - s * B;
-  out_idx[(size_t)b * S + s] = v_offset + (bi == kIdxNone ? 0 : bi);
-  if (out_val) out_val[(size_t)b * S + s] = bv;
+  out_idx[(size_t)b * S + s] = v_offset + idx;
+  if (out_val) out_val[(size_t)b * S + s] = v;
 }
 
 }  // namespace fmms

@@ -186,8 +186,9 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  // candidate rows of this CTA start as "none": two rows (one per epilogue warpgroup)
-  {
+  // S > 1 keeps the running candidates of each (row, draw) in global memory: two rows per CTA
+  // (one per epilogue warpgroup), which start as "none"
+  if (p.S > 1) {
     const int n = 2 * p.S * p.B;
     float* cv = p.cand_val + (size_t)cta * n;
     int* ci = p.cand_idx + (size_t)cta * n;
@@ -399,17 +400,30 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[j]);
     }
-    if (S == 1 && row_ok) {
-      p.cand_val[slot_row + b] = best_val;
-      p.cand_idx[slot_row + b] = best_idx;
+    // merge this thread's winners into the per-(row, draw) keys
+    if (row_ok) {
+      if (S == 1) {
+        if (best_idx != kIdxNone) atomicMax(&p.keys[b], cand_key(best_val, best_idx));
+      } else {
+        for (int s = 0; s < S; ++s) {
+          const size_t o = slot_row + (size_t)s * p.B + b;
+          const int ci = p.cand_idx[o];
+          if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
+        }
+      }
     }
   }
 
   tc_fence_before();
+  __threadfence();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (!(p.flags & kFlagTwoStage)) {
+    volatile int* is_last = abort_flag + 1;
+    finish_sample(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last);
   }
 }
 

@@ -44,6 +44,8 @@ extern "C" {
 #define FMMS_FLAG_RETURN_LOGITS 4  /* also store fp32 logits (core.py RETURN_LOGITS, :568-573) */
 #define FMMS_FLAG_FORCE_GEMV 8     /* use the small-batch weight-streaming kernel              */
 #define FMMS_FLAG_FORCE_MMA 16     /* use the tcgen05 tensor-core kernel                       */
+#define FMMS_FLAG_TWO_STAGE 32     /* decode the winners in a second kernel (the reference's
+                                      stage 2, core.py:359-370) instead of the last CTA        */
 
 /* kernel paths reported by fmms_last_path() */
 #define FMMS_PATH_NONE 0
@@ -61,10 +63,12 @@ const char* fmms_strerror(int status);
  * num_sms_cached(), core.py:212-214. */
 int fmms_num_sms(int* num_sms);
 
-/* Bytes of scratch the sampling call needs for its per-CTA (max, index)
- * candidates. Replaces the per-call torch.empty of `maxs` / `maxs_idx`
- * [num_samples, cdiv(V,128), H] in core.py:262-270 (here: one candidate per
- * persistent CTA, not per vocabulary tile). */
+/* Bytes of scratch the sampling call needs. Replaces the per-call torch.empty of
+ * `maxs` / `maxs_idx` [num_samples, cdiv(V,128), H] in core.py:262-270. Here every
+ * CTA folds its winners into one packed 64-bit key per (row, draw) with atomicMax.
+ * THE WORKSPACE MUST BE ZERO BEFORE ITS FIRST USE (one cudaMemset when it is
+ * created); every call leaves it ready for the next one. After a call that reported
+ * FMMS_ERR_TIMEOUT, zero it again. */
 int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes);
 
 /*
@@ -86,7 +90,8 @@ int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes);
  *   logits_out    [B, V_local] fp32, written when FMMS_FLAG_RETURN_LOGITS
  *   out_idx       [B, S] int64 global token ids
  *   out_val       [B, S] fp32 winning perturbed logits (nullable)
- *   workspace     >= fmms_query_workspace() bytes, 256-byte aligned
+ *   workspace     >= fmms_query_workspace() bytes, 256-byte aligned, zeroed once
+ *                 when created (see fmms_query_workspace)
  */
 int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                 int V_local, int D, int B, int S, unsigned long long seed,
@@ -164,7 +169,9 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
  *   - all calls on a device share the one array: two calls whose kernels overlap on the
  *     GPU (different streams without an ordering between them) race on it.  Calls on
  *     one stream, or ordered by events, are safe.  The array keeps the last call's
- *     candidates; nothing in it needs clearing between calls.
+ *     running candidates; the part that must start at zero (packed winners, CTA
+ *     counter) is zero when the library is loaded and is zeroed again by each call's
+ *     last CTA, so the caller never clears anything.
  */
 int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                        int V_local, int D, int B, int S, unsigned long long seed,

@@ -165,7 +165,7 @@ def test_vocab_offset_shifts_ids_and_noise(fs):
             out = torch.empty((B, S), dtype=torch.int64, device=_dev())
             val = torch.empty((B, S), dtype=torch.float32, device=_dev())
             wsz = _lib.query_workspace(hi - lo, D, B, S)
-            ws_buf = torch.empty(wsz, dtype=torch.uint8, device=_dev())
+            ws_buf = torch.zeros(wsz, dtype=torch.uint8, device=_dev())  # zeroed once, as the header asks
             t = torch.tensor([0.8], device=_dev())
             hd = h.to(_dev())
             rc = _lib.load().fmms_sample(
@@ -204,6 +204,20 @@ def test_qwen_head_full_size_external_noise(fs):
     a = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=5, kernel="gemv")
     b = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=5, kernel="mma")
     assert torch.equal(a, b)
+    fs.check_status()
+
+
+def test_two_stage_mode_gives_the_same_ids(fs):
+    """FMMS_FLAG_TWO_STAGE: winners decoded by a separate second-stage kernel (the reference's
+    stage 2) instead of the last CTA of the sampling kernel."""
+    for kernel, (V, D, B, S) in (("gemv", (5000, 256, 3, 2)), ("mma", (9000, 264, 70, 3))):
+        w, h = _head(V, D, B, w_std=0.08, seed=4)
+        w, h = w.to(_dev()), h.to(_dev())
+        t = torch.tensor(0.9, device=_dev())
+        a = fs.fused_mm_sample(w, h, S, t, seed=31, kernel=kernel)
+        b = fs.fused_mm_sample(w, h, S, t, seed=31, kernel=kernel, two_stage=True)
+        c = fs.fused_mm_sample(w, h, S, t, seed=31, kernel=kernel)
+        assert torch.equal(a, b) and torch.equal(a, c)
     fs.check_status()
 
 

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol(lib):
 def test_workspace_query_and_bad_arguments(lib):
     from flashsampling_b200 import _lib
 
-    assert _lib.query_workspace(151936, 4096, 64, 1) >= 296 * 64 * 8
+    assert _lib.query_workspace(151936, 4096, 64, 1) >= 256 + 297 * 64 * 8
     assert _lib.query_workspace(100, 16, 2, 10_000) >= 296 * 2 * 10_000 * 8
     import ctypes
 

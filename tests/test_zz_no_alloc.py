@@ -47,7 +47,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     cases = [(6000, 256, 3, 4, 11, _lib.FLAG_FORCE_GEMV), (9000, 512, 200, 2, 12, _lib.FLAG_FORCE_MMA)]
     for V, D, B, S, seed, flags in cases:
         w, h = gaussian_head(V, D, B, 0.06, seed=seed, device=dev)
-        ws = torch.empty(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=dev)
+        ws = torch.zeros(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=dev)
         rc_a, ids_a, val_a = _call(lib, "fmms_sample", w, h, t, B, S, seed, flags, ws)
         rc_b, ids_b, val_b = _call(lib, "fmms_sample_static", w, h, t, B, S, seed, flags)
         assert rc_a == 0 and rc_b == 0, (rc_a, rc_b, _lib.strerror(rc_b))
