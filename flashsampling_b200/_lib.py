@@ -48,6 +48,14 @@ SIGNATURES = {
             c_void_p,  # stream
         ],
     ),
+    "fmms_sample_tp": (
+        c_int,
+        [
+            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_longlong, c_int,
+            c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
+            c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.c_uint, c_ulonglong,
+        ],
+    ),
     "fmms_last_path": (c_int, []),
     "fmms_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
     "fmms_tp_buffer_bytes": (c_int, [c_int, c_int, ctypes.POINTER(c_size_t)]),

@@ -181,17 +181,25 @@ def fused_mm_sample(
     nbytes = _lib.query_workspace(V, D, B, num_samples)
     ws = _workspace(dev, stream.cuda_stream, nbytes)
     status = _status_word(dev)
+    common = (
+        weights.data_ptr(), hidden_states.data_ptr(), temp_ptr, temp_stride, V, D, B, num_samples,
+        int(seed) & 0xFFFFFFFFFFFFFFFF, v_begin, flags, noise_ptr, noise_ld,
+        logits.data_ptr() if logits is not None else None, out.data_ptr(),
+        vals.data_ptr() if vals is not None else None, ws.data_ptr(), ws.numel(),
+        status.data_ptr(), stream.cuda_stream,
+    )
+    fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
+        and not two_stage
     with torch.cuda.device(dev):
-        rc = lib.fmms_sample(
-            weights.data_ptr(), hidden_states.data_ptr(), temp_ptr, temp_stride, V, D, B, num_samples,
-            int(seed) & 0xFFFFFFFFFFFFFFFF, v_begin, flags, noise_ptr, noise_ld,
-            logits.data_ptr() if logits is not None else None, out.data_ptr(),
-            vals.data_ptr() if vals is not None else None, ws.data_ptr(), ws.numel(),
-            status.data_ptr(), stream.cuda_stream,
-        )
-    _lib.check(rc, "fmms_sample")
+        if fused_tp:
+            # one launch: the sampling kernel's last CTA runs the NVLink exchange itself
+            rc = lib.fmms_sample_tp(*common, tp.rank, tp.size, exchange.max_items, exchange.ptrs,
+                                    exchange.next_epoch(), 0)
+        else:
+            rc = lib.fmms_sample(*common)
+    _lib.check(rc, "fmms_sample_tp" if fused_tp else "fmms_sample")
 
-    if tp.size > 1:
+    if tp.size > 1 and not fused_tp:
         out, vals = exchange.reduce(out, vals)
 
     result = (out,)

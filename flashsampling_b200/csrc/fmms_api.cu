@@ -11,9 +11,9 @@
 
 #include "../../include/fmms_b200.h"
 #include "fmms_common.cuh"
+#include "fmms_tp.cuh"
 #include "fmms_gemv.cuh"
 #include "fmms_umma.cuh"
-#include "fmms_tp.cuh"
 
 namespace fmms {
 
@@ -328,11 +328,18 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
   return FMMS_OK;
 }
 
-int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
-                int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
-                int flags, const float* ext_noise, long long noise_ld, float* logits_out,
-                long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
-                int* status_dev, void* stream_v) {
+struct TpArgs {
+  int rank, world, max_items;
+  void* const* peer_buffers;
+  unsigned int epoch;
+  unsigned long long wait_limit_ns;
+};
+
+static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                       int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                       int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                       long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                       int* status_dev, void* stream_v, const TpArgs* tpa) {
   g_last_path = FMMS_PATH_NONE;
   if (!W_bf16 || !H_bf16 || !out_idx || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
   const bool greedy = flags & FMMS_FLAG_GREEDY, ext = flags & FMMS_FLAG_EXT_NOISE;
@@ -376,6 +383,24 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
   p.out_idx = out_idx;
   p.out_val = out_val;
+  p.tp_world = 1;
+  if (tpa) {
+    if (tpa->world < 1 || tpa->world > kTpMaxWorld || tpa->rank < 0 || tpa->rank >= tpa->world || !tpa->peer_buffers)
+      return FMMS_ERR_BAD_ARG;
+    if ((long long)B * S > tpa->max_items || (flags & FMMS_FLAG_TWO_STAGE)) return FMMS_ERR_UNSUPPORTED;
+    p.tp_rank = tpa->rank;
+    p.tp_world = tpa->world;
+    p.tp_max_items = tpa->max_items;
+    p.tp_epoch = tpa->epoch;
+    p.tp_wait_ns = tpa->wait_limit_ns ? tpa->wait_limit_ns : kWaitLimitNs;
+    for (int r = 0; r < tpa->world; ++r) {
+      if (!tpa->peer_buffers[r]) return FMMS_ERR_BAD_ARG;
+      p.tp_peers.slots[r] = reinterpret_cast<TpRecord*>(tpa->peer_buffers[r]);
+      p.tp_peers.flags[r] = reinterpret_cast<unsigned int*>(
+          reinterpret_cast<unsigned char*>(tpa->peer_buffers[r]) +
+          (size_t)2 * tpa->world * tpa->max_items * sizeof(TpRecord));
+    }
+  }
   p.status_dev = status_dev;
 
   const bool can_gemv = gemv_eligible(*d, D, B, S);
@@ -406,6 +431,29 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
   }
   return FMMS_OK;
 }
+
+int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                int* status_dev, void* stream) {
+  return sample_impl(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
+                     ext_noise, noise_ld, logits_out, out_idx, out_val, workspace, workspace_bytes, status_dev,
+                     stream, nullptr);
+}
+
+int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                   int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                   int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                   long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                   int* status_dev, void* stream, int rank, int world, int max_items,
+                   void* const* peer_buffers, unsigned int epoch, unsigned long long wait_limit_ns) {
+  const TpArgs tpa{rank, world, max_items, peer_buffers, epoch, wait_limit_ns};
+  return sample_impl(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
+                     ext_noise, noise_ld, logits_out, out_idx, out_val, workspace, workspace_bytes, status_dev,
+                     stream, &tpa);
+}
+
 
 // ---- tensor-parallel exchange -----------------------------------------------------------
 int fmms_tp_buffer_bytes(int world, int max_items, size_t* bytes) {

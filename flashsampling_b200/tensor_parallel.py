@@ -68,7 +68,14 @@ class CollectiveExchange:
 
 
 class PeerExchange:
-    """Exchange kernel over NVLink peer memory (CUDA IPC buffers, epoch flags)."""
+    """Exchange over NVLink peer memory (CUDA IPC buffers, epoch flags).
+
+    ``fused = True``: the sampling kernel itself performs the exchange in its last CTA
+    (``fmms_sample_tp``); ``reduce`` is the stand-alone exchange kernel, used for calls that are
+    too large for the buffers and by the "p2p-unfused" mode.
+    """
+
+    fused = True
 
     def __init__(self, tp: TPInfo, device: torch.device, max_items: int = MAX_ITEMS):
         if device.type != "cuda":
@@ -106,6 +113,10 @@ class PeerExchange:
     def vocab_offset(self, v_local: int) -> int:
         return self.tp.rank * v_local
 
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
     def reduce(self, ids: torch.Tensor, vals: torch.Tensor):
         flat_ids, flat_vals = ids.reshape(-1), vals.reshape(-1)
         out_ids, out_vals = torch.empty_like(flat_ids), torch.empty_like(flat_vals)
@@ -139,11 +150,31 @@ class PeerExchange:
             self.own = None
 
 
+class _UnfusedView:
+    """A PeerExchange whose exchange always runs as its own kernel after the sampling kernel."""
+
+    fused = False
+
+    def __init__(self, inner: PeerExchange):
+        self.inner = inner
+        self.max_items = inner.max_items
+
+    def vocab_offset(self, v_local: int) -> int:
+        return self.inner.vocab_offset(v_local)
+
+    def reduce(self, ids, vals):
+        return self.inner.reduce(ids, vals)
+
+    def check_status(self) -> None:
+        self.inner.check_status()
+
+
 _exchanges: dict = {}
 
 
 def exchange_mode() -> str:
-    """"p2p" (default) or "nccl": set FMMS_TP_EXCHANGE to choose."""
+    """FMMS_TP_EXCHANGE: "p2p" (default: exchange inside the sampling kernel), "p2p-unfused"
+    (separate exchange kernel) or "nccl" (all_gather baseline)."""
     return os.environ.get("FMMS_TP_EXCHANGE", "p2p")
 
 
@@ -153,13 +184,22 @@ def get_exchange(tp: TPInfo, device: torch.device):
     key = (tp.rank, tp.size, str(device), mode)
     ex = _exchanges.get(key)
     if ex is None:
-        ex = PeerExchange(tp, device) if mode == "p2p" else CollectiveExchange(tp, device)
+        if mode in ("p2p", "p2p-unfused"):
+            # both peer modes share one set of buffers and one epoch counter
+            ex = _exchanges.get((tp.rank, tp.size, str(device), "p2p-buffers"))
+            if ex is None:
+                ex = PeerExchange(tp, device)
+                _exchanges[(tp.rank, tp.size, str(device), "p2p-buffers")] = ex
+            if mode == "p2p-unfused":
+                ex = _UnfusedView(ex)
+        else:
+            ex = CollectiveExchange(tp, device)
         _exchanges[key] = ex
     return ex
 
 
 def close_exchanges() -> None:
-    for ex in _exchanges.values():
+    for ex in set(_exchanges.values()):
         if isinstance(ex, PeerExchange):
             ex.close()
     _exchanges.clear()

@@ -125,6 +125,20 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
  * the in-kernel peer stores (core.py:614-632).
  */
 
+/* fmms_sample() with the exchange folded into the sampling kernel: the CTA that finishes last
+ * writes this rank's winners into every rank's buffer, signals, waits (bounded) for the peers
+ * and writes the global winners to out_idx / out_val - one launch per step and rank, no host
+ * barrier.  Arguments as fmms_sample() plus those of fmms_tp_exchange(); B * S must not exceed
+ * `max_items`.  Replaces fused_mm_sample_triton() with tp.size > 1 (core.py:250-260,
+ * :614-632, :323-340). */
+int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                   int V_local, int D, int B, int S, unsigned long long seed,
+                   long long v_global_offset, int flags, const float* ext_noise, long long noise_ld,
+                   float* logits_out, long long* out_idx, float* out_val, void* workspace,
+                   size_t workspace_bytes, int* status_dev, void* stream, int rank, int world,
+                   int max_items, void* const* peer_buffers, unsigned int epoch,
+                   unsigned long long wait_limit_ns);
+
 /* Size of one rank's symmetric buffer for `world` ranks and up to `max_items` (B * S)
  * items per step. */
 int fmms_tp_buffer_bytes(int world, int max_items, size_t* bytes);

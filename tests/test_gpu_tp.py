@@ -28,7 +28,7 @@ def _tp_worker(world):
         t = (torch.rand(B, generator=torch.Generator().manual_seed(1)) + 0.5).to(dev)
         full = fs.fused_mm_sample(w.to(dev), h.to(dev), S, t, seed=42, kernel=kernel)  # unsharded, on this GPU
         w_local = shard_weights(w, tp).contiguous().to(dev)
-        for mode in ("p2p", "nccl"):
+        for mode in ("p2p", "p2p-unfused", "nccl"):
             os.environ["FMMS_TP_EXCHANGE"] = mode
             for rep in range(3):  # repeated steps exercise epochs and slot parities
                 got = fs.fused_mm_sample(w_local, h.to(dev), S, t, seed=42, tp=tp, kernel=kernel)
