@@ -12,6 +12,7 @@ no CPU path: without the CUDA library or a GPU the call raises.
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 from typing import Callable, Protocol
 
@@ -31,7 +32,9 @@ __all__ = [
     "PROVIDERS",
 ]
 
+_nullcontext = contextlib.nullcontext()
 _workspaces: dict[tuple, torch.Tensor] = {}
+_ws_bytes: dict[tuple, int] = {}  # (B, S) -> workspace bytes (independent of V and D)
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -174,11 +177,13 @@ def fused_mm_sample(
         exchange = get_exchange(tp, dev)
         v_begin = exchange.vocab_offset(V)
     out = torch.empty((B, num_samples), dtype=torch.int64, device=dev)
-    need_vals = return_values or tp.size > 1
+    need_vals = return_values or (tp.size > 1 and not getattr(exchange, "fused", False))
     vals = torch.empty((B, num_samples), dtype=torch.float32, device=dev) if need_vals else None
 
     stream = torch.cuda.current_stream(dev)
-    nbytes = _lib.query_workspace(V, D, B, num_samples)
+    nbytes = _ws_bytes.get((B, num_samples))
+    if nbytes is None:
+        nbytes = _ws_bytes[(B, num_samples)] = _lib.query_workspace(V, D, B, num_samples)
     ws = _workspace(dev, stream.cuda_stream, nbytes)
     status = _status_word(dev)
     common = (
@@ -190,7 +195,7 @@ def fused_mm_sample(
     )
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
         and not two_stage
-    with torch.cuda.device(dev):
+    with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
         if fused_tp:
             # one launch: the sampling kernel's last CTA runs the NVLink exchange itself
             rc = lib.fmms_sample_tp(*common, tp.rank, tp.size, exchange.max_items, exchange.ptrs,

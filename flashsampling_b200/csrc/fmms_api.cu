@@ -160,6 +160,10 @@ static int umma_stage_cap() {
   static const int v = env_int("FMMS_UMMA_STAGES");
   return v;
 }
+static int umma_mt2_nt_cap() {
+  static const int v = env_int("FMMS_UMMA_MT2_NTCAP") == 128 ? 128 : 256;
+  return v;
+}
 
 static int gemv_stages(const DeviceInfo& d, int NB, int D) {
   int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : kGemvMaxStages;
@@ -210,7 +214,7 @@ static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wm, const CUtensorMa
 }
 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
-  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap());
+  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap());
   if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
   CUtensorMap wm, hm;
   int rc = get_tensor_map(W, p.V, p.D, pl.tile_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wm);
@@ -222,6 +226,19 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   rc = pl.mt == 1 ? launch_umma_mt<1>(d, wm, hm, p, pl, stream) : launch_umma_mt<2>(d, wm, hm, p, pl, stream);
   if (rc != kOk) return -rc;
   return pl.grid * 2;
+}
+
+// ---- measurement helper: evict L2 with a read-only sweep (leaves no dirty lines behind) ----
+__global__ void l2_sweep_kernel(const uint4* __restrict__ p, size_t n16, unsigned int* sink) {
+  unsigned int acc = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p + i));
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x9e3779b9u && sink) *sink = acc;  // keeps the loads alive; practically never true
 }
 
 // ---- built-in scratch for callers that cannot allocate --------------------------------
@@ -516,6 +533,16 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
   tp_exchange_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       local_idx, local_val, n_items, max_items, rank, world, peers, epoch,
       wait_limit_ns ? wait_limit_ns : kWaitLimitNs, out_idx, out_val, status_dev);
+  return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream) {
+  if (!buffer || bytes < 16 || ((uintptr_t)buffer & 15)) return FMMS_ERR_BAD_ARG;
+  DeviceInfo* d = nullptr;
+  const int rc = device_info(&d);
+  if (rc != kOk) return rc;
+  l2_sweep_kernel<<<d->num_sms * 8, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(buffer), bytes / 16, nullptr);
   return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
 }
 

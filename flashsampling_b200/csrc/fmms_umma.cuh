@@ -46,17 +46,21 @@ struct UmmaPlan {
 
 __host__ __device__ inline size_t umma_stage_bytes(int mt) { return (size_t)kUmmaWTileBytes + (size_t)mt * kUmmaHTileBytes; }
 
-__host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0) {
+__host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
+                                   int mt2_nt_cap = 256) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
-  pl.nt_cap = pl.mt == 1 ? 256 : 128;
+  // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
+  // overlapped) re-read the hidden states least; FMMS_UMMA_MT2_NTCAP=128 selects two
+  // double-buffered 128-column accumulators instead.
+  pl.nt_cap = pl.mt == 1 ? 256 : mt2_nt_cap;
   int grid = (V + 15) / 16;
   if (grid > num_sms) grid = num_sms;
   pl.grid = grid;
   // Tile height: minimise the rows the busiest CTA walks (tiles are dealt out in
   // contiguous, near-equal ranges).  Short tiles re-read the hidden-state operand
   // too often for the shared-memory bandwidth, so large vocabularies keep NT high.
-  const int nt_floor = pl.mt == 1 ? 128 : 96;
+  const int nt_floor = pl.nt_cap >= 256 ? 128 : 96;
   const int nt_min = ((long long)V >= (long long)grid * nt_floor) ? nt_floor : 16;
   long long best_cost = -1;
   for (int nt = nt_min; nt <= pl.nt_cap; nt += 16) {

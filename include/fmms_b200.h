@@ -104,6 +104,12 @@ int fmms_sample(const void* W_bf16, const void* H_bf16, const float* temperature
  * kernel and autotunes its tile shape, core.py:442-476). */
 int fmms_last_path(void);
 
+/* Measurement helper: read `bytes` of `buffer` once with streaming loads, which evicts the
+ * L2 cache without leaving dirty lines behind (a memset-based flush makes the next kernel pay
+ * for the write-back).  Counterpart of the 256 MB `cache.zero_()` flush of the reference's
+ * bench harness (bench/triton_benchmark_lib.py:237-249). */
+int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream);
+
 /* Host-only: the launch plan fmms_sample would use on a device with `num_sms`
  * SMs and `max_smem_bytes` of opt-in shared memory per block; needs no GPU.
  * plan[0] = FMMS_PATH_*, [1] = persistent CTAs, [2] = vocabulary rows per tile

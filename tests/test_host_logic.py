@@ -52,7 +52,7 @@ def test_launch_plan_covers_the_vocabulary(lib, V, D, B):
         assert pl["smem_bytes"] <= 232448
         assert pl["candidate_rows"] <= 320
         if pl["path"] == _lib.PATH_MMA:
-            assert pl["tile_rows"] % 16 == 0 and 16 <= pl["tile_rows"] <= (256 if B <= 128 else 128)
+            assert pl["tile_rows"] % 16 == 0 and 16 <= pl["tile_rows"] <= 256
             assert pl["m_tiles"] == (2 if B > 128 else 1)
             busiest = -(-pl["tiles_total"] // pl["grid"]) * pl["tile_rows"]
             if V >= 148 * 128:
