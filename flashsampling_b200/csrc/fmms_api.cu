@@ -20,7 +20,7 @@ namespace fmms {
 constexpr int kVersion = 1000;
 constexpr int kMaxParts = 320;      // upper bound on candidate rows in the workspace (2 per persistent CTA)
 constexpr int kMaxDevices = 16;
-constexpr int kGemvAutoMaxBatch = 4;  // auto-dispatch: batches up to this use the weight-streaming kernel
+constexpr int kGemvAutoMaxBatch = 3;  // auto-dispatch: batches up to this use the weight-streaming kernel (measured crossover)
 
 static thread_local int g_last_path = FMMS_PATH_NONE;
 
@@ -166,7 +166,8 @@ static int umma_mt2_nt_cap() {
 }
 
 static int gemv_stages(const DeviceInfo& d, int NB, int D) {
-  int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : kGemvMaxStages;
+  // about 96-128 KiB of W in flight per SM: 6 x 16 KiB or 4 x 32 KiB stages
+  int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : (gemv_rows_per_warp(NB) == 8 ? 4 : kGemvMaxStages);
   while (stages >= 3 && gemv_smem_bytes(NB, D, stages) > (size_t)d.max_smem_optin) --stages;
   return stages >= 3 ? stages : 0;
 }
@@ -177,9 +178,10 @@ static bool gemv_eligible(const DeviceInfo& d, int D, int B, int S) {
 
 static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream_t stream) {
   CUtensorMap map;
+  const int NB = p.B;
+  const int kGemvRows = gemv_rows(NB);
   int rc = get_tensor_map(W, p.V, p.D, kGemvRows, kGemvCols, CU_TENSOR_MAP_SWIZZLE_NONE, &map);
   if (rc != kOk) return -rc;
-  const int NB = p.B;
   p.stages = gemv_stages(d, NB, p.D);
   const size_t smem = gemv_smem_bytes(NB, p.D, p.stages);
   const int groups = (p.V + kGemvRows - 1) / kGemvRows;
@@ -322,6 +324,7 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
   if (flags & FMMS_FLAG_FORCE_MMA) use_gemv = false;
   for (int i = 0; i < 8; ++i) plan[i] = 0;
   if (use_gemv) {
+    const int kGemvRows = gemv_rows(B);
     const int groups = (V_local + kGemvRows - 1) / kGemvRows;
     plan[0] = FMMS_PATH_GEMV;
     plan[1] = groups < num_sms ? groups : num_sms;

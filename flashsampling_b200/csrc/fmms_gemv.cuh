@@ -19,13 +19,16 @@
 namespace fmms {
 
 constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvRowsPerWarp = 4;
-constexpr int kGemvRows = kGemvConsumerWarps * kGemvRowsPerWarp;  // 32 rows per group
-constexpr int kGemvCols = 256;                                    // columns per stage
-constexpr int kGemvStageBytes = kGemvRows * kGemvCols * 2;        // 16 KiB
+constexpr int kGemvCols = 256;  // columns per stage
+// Rows of a group that one warp owns: 8 for two to four batch rows (more independent
+// accumulation chains per warp and half the hidden-state reloads); 4 for a single row, where
+// the finer 32-row groups balance better over the SMs, and above four rows (registers).
+__host__ __device__ constexpr int gemv_rows_per_warp(int NB) { return (NB >= 2 && NB <= 4) ? 8 : 4; }
+__host__ __device__ constexpr int gemv_rows(int NB) { return kGemvConsumerWarps * gemv_rows_per_warp(NB); }
+__host__ __device__ constexpr int gemv_stage_bytes(int NB) { return gemv_rows(NB) * kGemvCols * 2; }
 constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer warp
 constexpr int kGemvMaxBatch = 8;
-constexpr int kGemvItemsPerLane = 4;  // (row, b, s) items a lane may own: 4 * NB * S <= 128
+constexpr int kGemvItemsPerLane = 8;  // (row, b, s) items a lane may own: rows_per_warp * NB * S <= 256
 constexpr int kGemvMaxStages = 6;  // ~96 KiB in flight per SM: deeper rings measured slower
 
 struct SampleParams {
@@ -137,7 +140,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
 __host__ __device__ inline int gemv_dpad(int D) { return (D + kGemvCols - 1) / kGemvCols * kGemvCols; }
 
 __host__ __device__ inline size_t gemv_smem_bytes(int NB, int D, int stages) {
-  return (size_t)stages * kGemvStageBytes + (size_t)NB * gemv_dpad(D) * 2 + 16 * (size_t)stages +
+  return (size_t)stages * gemv_stage_bytes(NB) + (size_t)NB * gemv_dpad(D) * 2 + 16 * (size_t)stages +
          kGemvConsumerWarps * 32 * 8 + 16;
 }
 
@@ -149,6 +152,10 @@ template <int NB>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int kGemvRowsPerWarp = gemv_rows_per_warp(NB);
+  constexpr int kGemvRows = gemv_rows(NB);
+  constexpr int kGemvStageBytes = gemv_stage_bytes(NB);
+  constexpr int kRowShift = (kGemvRowsPerWarp == 8) ? 3 : 2;
   const int stages = p.stages;
   const int KC = (p.D + kGemvCols - 1) / kGemvCols;
   const int Dpad = KC * kGemvCols;
@@ -227,19 +234,13 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   const bool ret_logits = (p.flags & kFlagReturnLogits) != 0;
   const int n_items = kGemvRowsPerWarp * NB * p.S;
 
-  int item_r[kGemvItemsPerLane], item_b[kGemvItemsPerLane], item_s[kGemvItemsPerLane];
-  bool item_ok[kGemvItemsPerLane];
-  float item_invT[kGemvItemsPerLane], best_val[kGemvItemsPerLane];
+  // Lane l owns the items i = j * 32 + l (j < kGemvItemsPerLane) of the warp's
+  // rows_per_warp x NB x S results: row r = i % rows_per_warp, then b, then s.  Only the running
+  // best of each item lives in registers; the coordinates are recomputed when needed.
+  float best_val[kGemvItemsPerLane];
   int best_idx[kGemvItemsPerLane];
 #pragma unroll
   for (int j = 0; j < kGemvItemsPerLane; ++j) {
-    const int i = j * 32 + lane;
-    item_r[j] = i & 3;
-    item_b[j] = (i >> 2) % NB;
-    item_s[j] = (i >> 2) / NB;
-    item_ok[j] = (i < n_items) && (item_b[j] < p.B);
-    item_invT[j] = 1.0f;
-    if (item_ok[j] && !greedy) item_invT[j] = 1.0f / p.temperature[(size_t)item_b[j] * p.temp_stride];
     best_val[j] = -INFINITY;
     best_idx[j] = kIdxNone;
   }
@@ -301,24 +302,31 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     const int v_warp = g * kGemvRows + warp * kGemvRowsPerWarp;
 #pragma unroll
     for (int j = 0; j < kGemvItemsPerLane; ++j) {
-      const int v = v_warp + item_r[j];
-      if (item_ok[j] && v < p.V) {
+      const int i = j * 32 + lane;
+      const int item_r = i & (kGemvRowsPerWarp - 1);
+      const int item_b = (i >> kRowShift) % NB;
+      const int item_s = (i >> kRowShift) / NB;
+      const int v = v_warp + item_r;
+      if (i < n_items && item_b < p.B && v < p.V) {
         float val = 0.f;
 #pragma unroll
         for (int r = 0; r < kGemvRowsPerWarp; ++r)
 #pragma unroll
           for (int b = 0; b < NB; ++b)
-            if (item_r[j] == r && item_b[j] == b) val = sum[r][b];
-        if (ret_logits && item_s[j] == 0) p.logits_out[(size_t)item_b[j] * p.V + v] = val;
+            if (item_r == r && item_b == b) val = sum[r][b];
+        if (ret_logits && item_s == 0) p.logits_out[(size_t)item_b * p.V + v] = val;
         float y;
         if (greedy) {
           y = val;
-        } else if (ext) {
-          y = fmaf(val, item_invT[j], p.ext_noise[((size_t)item_s[j] * p.B + item_b[j]) * p.noise_ld + v]);
         } else {
-          const unsigned long long vg = (unsigned long long)(p.v_offset + v);
-          const uint4 q = noise_block(p.seed, item_s[j], item_b[j], vg >> 2);
-          y = fmaf(val, item_invT[j], gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+          const float inv_t = 1.0f / p.temperature[(size_t)item_b * p.temp_stride];
+          if (ext) {
+            y = fmaf(val, inv_t, p.ext_noise[((size_t)item_s * p.B + item_b) * p.noise_ld + v]);
+          } else {
+            const unsigned long long vg = (unsigned long long)(p.v_offset + v);
+            const uint4 q = noise_block(p.seed, item_s, item_b, vg >> 2);
+            y = fmaf(val, inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+          }
         }
         if (y > best_val[j]) {
           best_val[j] = y;
@@ -328,11 +336,11 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     }
   }
 
-  // ---- CTA-level reduction of the running candidates: rows (2 shuffles), warps (smem) ----
+  // ---- CTA-level reduction of the running candidates: rows (shuffles), warps (smem) ----
 #pragma unroll
   for (int j = 0; j < kGemvItemsPerLane; ++j) {
 #pragma unroll
-    for (int off = 1; off <= 2; off <<= 1) {
+    for (int off = 1; off < kGemvRowsPerWarp; off <<= 1) {
       const float v2 = __shfl_xor_sync(0xffffffffu, best_val[j], off);
       const int i2 = __shfl_xor_sync(0xffffffffu, best_idx[j], off);
       cand_merge(best_val[j], best_idx[j], v2, i2);
@@ -342,9 +350,9 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
 #pragma unroll
   for (int j = 0; j < kGemvItemsPerLane; ++j) {
     const int i = j * 32 + lane;
-    if ((i & 3) == 0 && (i >> 2) < n_slots) {
-      red_val[warp * 32 + (i >> 2)] = best_val[j];
-      red_idx[warp * 32 + (i >> 2)] = best_idx[j];
+    if ((i & (kGemvRowsPerWarp - 1)) == 0 && (i >> kRowShift) < n_slots) {
+      red_val[warp * 32 + (i >> kRowShift)] = best_val[j];
+      red_idx[warp * 32 + (i >> kRowShift)] = best_idx[j];
     }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory");

@@ -197,9 +197,12 @@ def test_qwen_head_full_size_external_noise(fs):
     ids = fs.fused_mm_sample(wd, h.to(_dev()), 1, t, seed=0, noise=noise.to(_dev()))
     assert fs.last_path() == "mma"
     _check_indices(ids, logits, 0.7, noise, "qwen B=64")
-    ids4 = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=0, noise=noise[:4].contiguous().to(_dev()))
-    assert fs.last_path() == "gemv"
+    ids4 = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=0, noise=noise[:4].contiguous().to(_dev()),
+                              kernel="gemv")
     _check_indices(ids4, logits[:4], 0.7, noise[:4], "qwen B=4")
+    ids2 = fs.fused_mm_sample(wd, h[:2].contiguous().to(_dev()), 1, t, seed=0, noise=noise[:2].contiguous().to(_dev()))
+    assert fs.last_path() == "gemv"
+    _check_indices(ids2, logits[:2], 0.7, noise[:2], "qwen B=2", min_decisive=0.5)
     # seeded full-size draws: the two kernels see the same noise stream
     a = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=5, kernel="gemv")
     b = fs.fused_mm_sample(wd, h[:4].contiguous().to(_dev()), 1, t, seed=5, kernel="mma")

@@ -58,7 +58,7 @@ def test_launch_plan_covers_the_vocabulary(lib, V, D, B):
             if V >= 148 * 128:
                 assert busiest <= 1.15 * V / pl["grid"] + 16, "tile choice leaves the busiest CTA too much work"
         else:
-            assert B <= 8 and pl["tile_rows"] == 32 and pl["stages"] >= 3
+            assert B <= 8 and pl["tile_rows"] == (64 if 2 <= B <= 4 else 32) and pl["stages"] >= 3
 
 
 def test_plan_dispatch_rules(lib):
