@@ -21,7 +21,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -55,53 +54,64 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Polls SM clock, power and throttle reasons of one GPU through NVML (read-only) from a
+    background thread while the timed region runs; falls back to an empty summary without NVML."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, cuda_index: int, period_s: float = 0.002):
+        self.cuda_index, self.period = cuda_index, period_s
+        self.samples, self.reasons, self.power = [], set(), []
+        self.stop_flag = threading.Event()
+        self.handle = self.nvml = None
+        self.sm_max = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.nvml = pynvml
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                self.power.append(n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+                mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
-
     def __exit__(self, *exc):
-        if self.proc:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=2)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self.stop_flag.set()
+        if self.handle is not None:
+            self.thread.join(timeout=1.0)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, val in zip(names, r[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.sm_max,
+                "power_w_max": round(max(self.power), 1) if self.power else None,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
 def make_inputs(wl, B, rank, world, device):
@@ -378,10 +388,30 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_once(args):
+    """--once: build the workload and make a handful of sampling calls (a read-only L2 sweep before
+    each), nothing else.  This is the command profiled under ncu for the summaries in profiles/."""
+    import flashsampling_b200 as fs
+    from flashsampling_b200 import _lib, build
+
+    build.build_library()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    wl = WORKLOADS[args.workload]
+    w, h, t = make_inputs(wl, args.batch, 0, 1, device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for i in range(5):
+        _lib.load().fmms_l2_sweep(flush.data_ptr(), flush.numel(), torch.cuda.current_stream().cuda_stream)
+        fs.fused_mm_sample(w, h, wl["S"], t, seed=i, kernel=args.kernel)
+    torch.cuda.synchronize()
+    fs.check_status()
+    print(json.dumps({"once": True, "workload": args.workload, "batch": args.batch, "kernel": fs.last_path()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=25)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="qwen", choices=sorted(WORKLOADS))
@@ -389,8 +419,12 @@ def main():
     ap.add_argument("--sweep", action=argparse.BooleanOptionalAction, default=True)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--once", action="store_true", help="five calls of one configuration, for profilers")
+    ap.add_argument("--kernel", default=None, choices=["gemv", "mma"], help="--once: force a kernel")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.once:
+        run_once(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -126,7 +126,7 @@ def query_workspace(v_local: int, d: int, b: int, s: int) -> int:
     return int(n.value)
 
 
-PLAN_FIELDS = ("path", "grid", "tile_rows", "tiles_total", "stages", "m_tiles", "smem_bytes", "candidate_rows")
+PLAN_FIELDS = ("path", "grid", "tile_rows", "tiles_per_cta", "stages", "m_tiles", "smem_bytes", "candidate_rows")
 
 
 def plan(v_local: int, d: int, b: int, s: int, flags: int = 0, num_sms: int = 148, max_smem: int = 232448) -> dict:

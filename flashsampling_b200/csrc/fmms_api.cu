@@ -203,29 +203,36 @@ static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream
 
 // ---- tensor-core launch -----------------------------------------------------------
 template <int MT>
-static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wm, const CUtensorMap& hm, SampleParams& p,
-                          const UmmaPlan& pl, cudaStream_t stream) {
+static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wq, const CUtensorMap& wq1, const CUtensorMap& hm,
+                          SampleParams& p, const UmmaPlan& pl, cudaStream_t stream) {
   if (!d.umma_attr[MT]) {
     if (cudaFuncSetAttribute(umma_sample_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              d.max_smem_optin) != cudaSuccess)
       return kErrCuda;
     d.umma_attr[MT] = true;
   }
-  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wm, hm, p, pl.nt_cap, pl.tiles_total, pl.h_rows);
+  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.nt_cap, pl.units_total,
+                                                                     pl.q_units, pl.h_rows);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
   const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap());
   if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
-  CUtensorMap wm, hm;
-  int rc = get_tensor_map(W, p.V, p.D, pl.tile_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wm);
+  CUtensorMap wq, wq1, hm;
+  int rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wq);
   if (rc != kOk) return -rc;
+  wq1 = wq;  // a CTA only uses the lower box when some tile is one unit shorter
+  if (pl.q_units > 1) {
+    rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wq1);
+    if (rc != kOk) return -rc;
+  }
   rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &hm);
   if (rc != kOk) return -rc;
   p.stages = pl.stages;
-  p.tile_rows = pl.tile_rows;
-  rc = pl.mt == 1 ? launch_umma_mt<1>(d, wm, hm, p, pl, stream) : launch_umma_mt<2>(d, wm, hm, p, pl, stream);
+  p.tile_rows = pl.q_units * 16;
+  p.tiles_per_cta = pl.tiles_per_cta;
+  rc = pl.mt == 1 ? launch_umma_mt<1>(d, wq, wq1, hm, p, pl, stream) : launch_umma_mt<2>(d, wq, wq1, hm, p, pl, stream);
   if (rc != kOk) return -rc;
   return pl.grid * 2;
 }
@@ -329,7 +336,7 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
     plan[0] = FMMS_PATH_GEMV;
     plan[1] = groups < num_sms ? groups : num_sms;
     plan[2] = kGemvRows;
-    plan[3] = groups;
+    plan[3] = (groups + plan[1] - 1) / plan[1];
     plan[4] = gemv_stages(d, B, D);
     plan[5] = 1;
     plan[6] = (int)gemv_smem_bytes(B, D, plan[4]);
@@ -338,8 +345,8 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
     const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes);
     plan[0] = FMMS_PATH_MMA;
     plan[1] = pl.grid;
-    plan[2] = pl.tile_rows;
-    plan[3] = pl.tiles_total;
+    plan[2] = pl.q_units * 16;
+    plan[3] = pl.tiles_per_cta;
     plan[4] = pl.stages;
     plan[5] = pl.mt;
     plan[6] = (int)pl.smem;

@@ -28,7 +28,6 @@ __host__ __device__ constexpr int gemv_rows(int NB) { return kGemvConsumerWarps 
 __host__ __device__ constexpr int gemv_stage_bytes(int NB) { return gemv_rows(NB) * kGemvCols * 2; }
 constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer warp
 constexpr int kGemvMaxBatch = 8;
-constexpr int kGemvItemsPerLane = 8;  // (row, b, s) items a lane may own: rows_per_warp * NB * S <= 256
 constexpr int kGemvMaxStages = 6;  // ~96 KiB in flight per SM: deeper rings measured slower
 
 struct SampleParams {
@@ -156,6 +155,8 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   constexpr int kGemvRows = gemv_rows(NB);
   constexpr int kGemvStageBytes = gemv_stage_bytes(NB);
   constexpr int kRowShift = (kGemvRowsPerWarp == 8) ? 3 : 2;
+  // (row, b, s) results a lane may own: rows_per_warp * NB * S <= rows_per_warp * 32
+  constexpr int kGemvItemsPerLane = kGemvRowsPerWarp;
   const int stages = p.stages;
   const int KC = (p.D + kGemvCols - 1) / kGemvCols;
   const int Dpad = KC * kGemvCols;

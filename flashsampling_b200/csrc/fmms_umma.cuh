@@ -34,45 +34,37 @@ constexpr int kUmmaHTileBytes = 128 * 128;  // one 128-row hidden-state tile
 constexpr int kTmemCols = 512;
 
 struct UmmaPlan {
-  int grid;         // persistent CTAs
-  int tile_rows;    // NT: vocabulary rows per tile (multiple of 16, <= nt_cap)
-  int nt_cap;       // TMEM columns reserved per accumulator (256 or 128)
-  int tiles_total;  // ceil(V / NT)
-  int stages;       // shared-memory ring depth
-  int h_rows;       // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
-  int mt;           // M tiles (1 or 2)
+  int grid;           // persistent CTAs
+  int units_total;    // ceil(V / 16): the vocabulary in units of 16 rows (the MMA N granule)
+  int tiles_per_cta;  // T: every CTA cuts its contiguous range of units into T tiles
+  int q_units;        // tiles are q_units or q_units - 1 units high
+  int nt_cap;         // TMEM columns reserved per accumulator (256 or 128)
+  int stages;         // shared-memory ring depth
+  int h_rows;         // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
+  int mt;             // M tiles (1 or 2)
   size_t smem;
 };
 
 __host__ __device__ inline size_t umma_stage_bytes(int mt) { return (size_t)kUmmaWTileBytes + (size_t)mt * kUmmaHTileBytes; }
 
+// Work split.  The vocabulary is dealt out in units of 16 rows: CTA c gets a contiguous range
+// of U_c = units_total / grid (+1 for the first units_total % grid CTAs) units and cuts it into
+// T near-equal tiles, so no CTA walks more than 16 rows beyond the average.  All tiles of all
+// CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
                                    int mt2_nt_cap = 256) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
-  // overlapped) re-read the hidden states least; FMMS_UMMA_MT2_NTCAP=128 selects two
-  // double-buffered 128-column accumulators instead.
+  // overlapped) re-read the hidden states least; mt2_nt_cap = 128 selects two double-buffered
+  // 128-column accumulators instead.
   pl.nt_cap = pl.mt == 1 ? 256 : mt2_nt_cap;
-  int grid = (V + 15) / 16;
-  if (grid > num_sms) grid = num_sms;
-  pl.grid = grid;
-  // Tile height: minimise the rows the busiest CTA walks (tiles are dealt out in
-  // contiguous, near-equal ranges).  Short tiles re-read the hidden-state operand
-  // too often for the shared-memory bandwidth, so large vocabularies keep NT high.
-  const int nt_floor = pl.nt_cap >= 256 ? 128 : 96;
-  const int nt_min = ((long long)V >= (long long)grid * nt_floor) ? nt_floor : 16;
-  long long best_cost = -1;
-  for (int nt = nt_min; nt <= pl.nt_cap; nt += 16) {
-    const int tiles = (V + nt - 1) / nt;
-    const long long cost = (long long)((tiles + grid - 1) / grid) * nt;
-    if (best_cost < 0 || cost <= best_cost) {  // ties: prefer the larger tile
-      best_cost = cost;
-      pl.tile_rows = nt;
-      pl.tiles_total = tiles;
-    }
-  }
-  if (pl.tiles_total < pl.grid) pl.grid = pl.tiles_total;
+  pl.units_total = (V + 15) / 16;
+  pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
+  const int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
+  const int cap_units = pl.nt_cap / 16;
+  pl.tiles_per_cta = (u_max + cap_units - 1) / cap_units;
+  pl.q_units = (u_max + pl.tiles_per_cta - 1) / pl.tiles_per_cta;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
   const size_t fixed = 1024 /*barriers etc.*/ + 1024 /*alignment slack*/;
   int stages = stages_cap > 1 ? stages_cap : 6;
@@ -81,6 +73,29 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.smem = stages * umma_stage_bytes(pl.mt) + fixed;
   return pl;
 }
+
+// The tile schedule of one CTA, recomputed identically by every warp role.
+struct TileWalk {
+  int u_next;    // first unit of the next tile
+  int base, extra, i;
+  __device__ __forceinline__ TileWalk(int units_total, int T) {
+    const int per = units_total / (int)gridDim.x, rem = units_total % (int)gridDim.x;
+    const int c = blockIdx.x;
+    const int u_cnt = per + (c < rem ? 1 : 0);
+    u_next = c * per + min(c, rem);
+    base = u_cnt / T;
+    extra = u_cnt % T;
+    i = 0;
+  }
+  // rows of tile i (0 when this CTA has fewer units than tiles) and its first vocabulary row
+  __device__ __forceinline__ void next(int& v0, int& nt) {
+    const int units = base + (i < extra ? 1 : 0);
+    v0 = u_next * 16;
+    nt = units * 16;
+    u_next += units;
+    ++i;
+  }
+};
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -150,12 +165,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // ---- the kernel ------------------------------------------------------------------
 template <int MT>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
-umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap h_map,
-                   const SampleParams p, const int nt_cap, const int tiles_total, const int h_rows) {
+umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
+                   const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
+                   const int units_total, const int q_units, const int h_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
-  const int NT = p.tile_rows;
+  const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
   const size_t stage_bytes = umma_stage_bytes(MT);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes);
   uint64_t* empty_bar = full_bar + stages;
@@ -168,11 +184,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   const int acc_stages = kTmemCols / (MT * nt_cap);
   const int KB = (p.D + kUmmaBK - 1) / kUmmaBK;
 
-  // contiguous tile range of this CTA
-  const int base = tiles_total / (int)gridDim.x, rem = tiles_total % (int)gridDim.x;
   const int cta = blockIdx.x;
-  const int t_begin = cta * base + min(cta, rem);
-  const int n_tiles = base + (cta < rem ? 1 : 0);
 
   if (tid == 0) {
     for (int i = 0; i < stages; ++i) {
@@ -213,13 +225,22 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     // operations per microsecond, which would cap the weight stream.
     if (lane == 0) {
       const bool is_w = (warp == 0);
-      prefetch_tmap(is_w ? &w_map : &h_map);
+      if (is_w) {
+        prefetch_tmap(&w_map_q);
+        prefetch_tmap(&w_map_q1);
+      } else {
+        prefetch_tmap(&h_map);
+      }
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
-      const uint32_t tx = is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u;
       int it = 0;
       bool ok = true;
+      TileWalk walk(units_total, n_tiles);
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int v0 = (t_begin + t) * NT;
+        int v0, NT;
+        walk.next(v0, NT);
+        if (NT == 0) continue;
+        const uint32_t tx = is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u;
+        const CUtensorMap* wm = (NT == q_units * 16) ? &w_map_q : &w_map_q1;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int st = it % stages;
           const uint32_t n = (uint32_t)(it / stages);
@@ -230,7 +251,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           uint8_t* sw = smem + st * stage_bytes;
           mbar_arrive_expect_tx(&full_bar[st], tx);
           if (is_w) {
-            tma_load_2d_hint(sw, &w_map, kb * kUmmaBK, v0, &full_bar[st], pol);
+            tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
           } else {
 #pragma unroll
             for (int m = 0; m < MT; ++m)
@@ -249,12 +270,17 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(NT);
       int it = 0;
       bool ok = true;
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int j = t % acc_stages;
-        const uint32_t un = (uint32_t)(t / acc_stages);
+      TileWalk walk(units_total, n_tiles);
+      for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
+        int v0, NT;
+        walk.next(v0, NT);
+        if (NT == 0) continue;
+        const uint32_t idesc = umma_idesc(NT);
+        const int j = ta % acc_stages;
+        const uint32_t un = (uint32_t)(ta / acc_stages);
+        ++ta;
         if (!mbar_wait(&acc_empty[j], (un & 1u) ^ 1u, abort_flag, p.status_dev)) break;
         tc_fence_after();
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -292,10 +318,6 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     const int b = m_tile * 128 + quad * 32 + lane;
     const bool row_ok = b < p.B;
     const bool warp_ok = (m_tile * 128 + quad * 32) < p.B;
-    // column range of this warp inside a tile: MT = 1 splits the tile between the warpgroups
-    const int half = ((NT / 2) + 31) / 32 * 32;
-    const int c_begin = (MT == 2) ? 0 : (wg == 0 ? 0 : min(half, NT));
-    const int c_end = (MT == 2) ? NT : (wg == 0 ? min(half, NT) : NT);
 
     const bool greedy = (p.flags & kFlagGreedy) != 0;
     const bool ext = (p.flags & kFlagExtNoise) != 0;
@@ -309,13 +331,21 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
 
-    for (int t = 0; t < n_tiles; ++t) {
-      const int j = t % acc_stages;
-      const uint32_t un = (uint32_t)(t / acc_stages);
+    TileWalk walk(units_total, n_tiles);
+    for (int t = 0, ta = 0; t < n_tiles; ++t) {
+      int v0, NT;
+      walk.next(v0, NT);
+      if (NT == 0) continue;
+      // column range of this warp inside the tile: MT = 1 splits the tile between the warpgroups
+      const int half = ((NT / 2) + 31) / 32 * 32;
+      const int c_begin = (MT == 2) ? 0 : (wg == 0 ? 0 : min(half, NT));
+      const int c_end = (MT == 2) ? NT : (wg == 0 ? min(half, NT) : NT);
+      const int j = ta % acc_stages;
+      const uint32_t un = (uint32_t)(ta / acc_stages);
+      ++ta;
       if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
       tc_fence_after();
       if (warp_ok) {
-        const int v0 = (t_begin + t) * NT;
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         for (int s = 0; s < S; ++s) {
           float bv = best_val;

@@ -112,8 +112,8 @@ int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream);
 
 /* Host-only: the launch plan fmms_sample would use on a device with `num_sms`
  * SMs and `max_smem_bytes` of opt-in shared memory per block; needs no GPU.
- * plan[0] = FMMS_PATH_*, [1] = persistent CTAs, [2] = vocabulary rows per tile
- * (row group), [3] = tiles in total, [4] = pipeline stages, [5] = M tiles,
+ * plan[0] = FMMS_PATH_*, [1] = persistent CTAs, [2] = vocabulary rows of the tallest tile
+ * (row group), [3] = tiles (row groups) of the busiest CTA, [4] = pipeline stages, [5] = M tiles,
  * [6] = dynamic shared memory bytes, [7] = candidate rows handed to the
  * cross-CTA reduction.  Replaces the tile heuristics bsz_h() (core.py:876-881)
  * and the autotune table (core.py:442-470). */
