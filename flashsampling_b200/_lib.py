@@ -58,6 +58,7 @@ SIGNATURES = {
     ),
     "fmms_last_path": (c_int, []),
     "fmms_l2_sweep": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "fmms_debug_stamps": (c_int, [c_void_p]),
     "fmms_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
     "fmms_tp_buffer_bytes": (c_int, [c_int, c_int, ctypes.POINTER(c_size_t)]),
     "fmms_tp_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),

@@ -23,6 +23,7 @@ constexpr int kMaxDevices = 16;
 constexpr int kGemvAutoMaxBatch = 3;  // auto-dispatch: batches up to this use the weight-streaming kernel (measured crossover)
 
 static thread_local int g_last_path = FMMS_PATH_NONE;
+static unsigned long long* g_stamps = nullptr;  // see fmms_debug_stamps()
 
 struct DeviceInfo {
   bool ready = false;
@@ -160,6 +161,14 @@ static int umma_stage_cap() {
   static const int v = env_int("FMMS_UMMA_STAGES");
   return v;
 }
+static int umma_nt_target() {
+  static const int v = env_int("FMMS_UMMA_NT");
+  return v;
+}
+static int umma_min_tiles() {
+  static const int v = env_int("FMMS_UMMA_MIN_TILES") > 0 ? env_int("FMMS_UMMA_MIN_TILES") : 1;
+  return v;
+}
 static int umma_mt2_nt_cap() {
   static const int v = env_int("FMMS_UMMA_MT2_NTCAP") == 128 ? 128 : 256;
   return v;
@@ -217,7 +226,7 @@ static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wq, const CUtensorMa
 }
 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
-  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap());
+  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(), umma_min_tiles());
   if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
   CUtensorMap wq, wq1, hm;
   int rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wq);
@@ -429,6 +438,7 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
     }
   }
   p.status_dev = status_dev;
+  p.stamps = g_stamps;
 
   const bool can_gemv = gemv_eligible(*d, D, B, S);
   bool use_gemv;
@@ -544,6 +554,11 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
       local_idx, local_val, n_items, max_items, rank, world, peers, epoch,
       wait_limit_ns ? wait_limit_ns : kWaitLimitNs, out_idx, out_val, status_dev);
   return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+int fmms_debug_stamps(unsigned long long* stamps_dev) {
+  g_stamps = stamps_dev;
+  return FMMS_OK;
 }
 
 int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream) {

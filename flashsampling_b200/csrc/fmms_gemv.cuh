@@ -48,6 +48,7 @@ struct SampleParams {
   long long* out_idx;        // [B, S]
   float* out_val;            // [B, S] or null
   int* status_dev;
+  unsigned long long* stamps;  // optional [gridDim.x][8] %globaltimer stamps of the kernel's phases (null = off)
   int stages;                // shared-memory ring depth
   int tile_rows;             // tensor-core path: vocabulary rows per tile
   int tiles_per_cta;         // tensor-core path
@@ -61,6 +62,10 @@ struct SampleParams {
 // Last step of a sampling kernel, run by `nthreads` threads of every CTA after their packed
 // candidates went into p.keys with atomicMax: the CTA that takes the last ticket decodes the
 // winners into the output and leaves keys and ticket zero for the next launch.
+__device__ __forceinline__ void stamp(const SampleParams& p, int slot) {
+  if (p.stamps) p.stamps[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
+}
+
 template <class SyncFn>
 __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, int nthreads, SyncFn sync,
                                               volatile int* is_last) {
@@ -68,6 +73,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   sync();
   if (tid == 0) *is_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
   sync();
+  if (tid == 0) stamp(p, 6);
   if (!*is_last) return;
   __threadfence();
   const int n = p.B * p.S;
@@ -82,6 +88,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
       if (p.out_val) p.out_val[(size_t)b * p.S + s] = v;
     }
     if (tid == 0) *p.ticket = 0u;
+    if (tid == 0) stamp(p, 7);
     return;
   }
   // Tensor parallel: this rank's winners go straight into every rank's exchange buffer (see
@@ -186,6 +193,7 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     }
     *abort_flag = 0;
     fence_mbar_init();
+    stamp(p, 0);
   }
   // hidden states -> shared memory, zero padded to [NB][Dpad]
   {
@@ -337,6 +345,7 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     }
   }
 
+  if (tid == 0) stamp(p, 5);
   // ---- CTA-level reduction of the running candidates: rows (shuffles), warps (smem) ----
 #pragma unroll
   for (int j = 0; j < kGemvItemsPerLane; ++j) {

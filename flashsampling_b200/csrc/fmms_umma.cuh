@@ -29,8 +29,8 @@ constexpr int kUmmaThreads = 384;
 constexpr int kUmmaEpiWarp0 = 4;       // first epilogue warp
 constexpr int kUmmaEpiWarps = 8;       // two warpgroups
 constexpr int kUmmaBK = 64;            // hidden-dimension slice per stage (128 B of bf16)
-constexpr int kUmmaWTileBytes = 256 * 128;  // room for a 256-row W tile per stage
-constexpr int kUmmaHTileBytes = 128 * 128;  // one 128-row hidden-state tile
+constexpr int kUmmaHTileMax = 128 * 128;  // the MMA always reads 128 hidden-state rows (16 KiB)
+constexpr int kUmmaMaxStages = 12;
 constexpr int kTmemCols = 512;
 
 struct UmmaPlan {
@@ -45,14 +45,20 @@ struct UmmaPlan {
   size_t smem;
 };
 
-__host__ __device__ inline size_t umma_stage_bytes(int mt) { return (size_t)kUmmaWTileBytes + (size_t)mt * kUmmaHTileBytes; }
+// Shared memory: [barriers 1 KiB][stages x (W tile: tallest tile x 128 B | MT hidden-state tiles:
+// h_rows x 128 B)][16 KiB slack].  With fewer than 128 hidden-state rows the MMA's 128-row A
+// operand runs past its tile into whatever follows (the next stage, or the slack after the last
+// one); those accumulator lanes belong to no batch row and are never read.
+__host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows) {
+  return (size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128;
+}
 
 // Work split.  The vocabulary is dealt out in units of 16 rows: CTA c gets a contiguous range
 // of U_c = units_total / grid (+1 for the first units_total % grid CTAs) units and cuts it into
 // T near-equal tiles, so no CTA walks more than 16 rows beyond the average.  All tiles of all
 // CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
-                                   int mt2_nt_cap = 256) {
+                                   int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
@@ -62,15 +68,22 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.units_total = (V + 15) / 16;
   pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
   const int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
-  const int cap_units = pl.nt_cap / 16;
+  int cap_units = pl.nt_cap / 16;
+  if (nt_target >= 16 && nt_target / 16 < cap_units) cap_units = nt_target / 16;
   pl.tiles_per_cta = (u_max + cap_units - 1) / cap_units;
+  // min_tiles > 1 cuts small per-CTA ranges into several tiles so that epilogues overlap the next
+  // mainloop; measured slower on the small shards of 8-way tensor parallelism, because W boxes
+  // under ~16 KiB run into the per-thread TMA issue rate.
+  if (pl.tiles_per_cta < min_tiles && u_max >= 4 * min_tiles) pl.tiles_per_cta = min_tiles;
   pl.q_units = (u_max + pl.tiles_per_cta - 1) / pl.tiles_per_cta;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
-  const size_t fixed = 1024 /*barriers etc.*/ + 1024 /*alignment slack*/;
-  int stages = stages_cap > 1 ? stages_cap : 6;
-  while (stages > 2 && stages * umma_stage_bytes(pl.mt) + fixed > (size_t)max_smem) --stages;
+  const size_t fixed = 1024 /*barriers*/ + 1024 /*alignment*/ + kUmmaHTileMax /*A-operand overrun*/;
+  const size_t sb = umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows);
+  int stages = stages_cap > 1 ? stages_cap : kUmmaMaxStages;
+  if (stages > kUmmaMaxStages) stages = kUmmaMaxStages;
+  while (stages > 2 && stages * sb + fixed > (size_t)max_smem) --stages;
   pl.stages = stages;
-  pl.smem = stages * umma_stage_bytes(pl.mt) + fixed;
+  pl.smem = stages * sb + fixed;
   return pl;
 }
 
@@ -172,8 +185,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
-  const size_t stage_bytes = umma_stage_bytes(MT);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes);
+  const size_t w_tile_bytes = (size_t)q_units * 16 * 128, h_tile_bytes = (size_t)h_rows * 128;
+  const size_t stage_bytes = w_tile_bytes + MT * h_tile_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
+  smem += 1024;  // stages start 1 KiB-aligned behind the barriers
   uint64_t* empty_bar = full_bar + stages;
   uint64_t* acc_full = empty_bar + stages;
   uint64_t* acc_empty = acc_full + 4;
@@ -197,6 +212,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     *abort_flag = 0;
     fence_mbar_init();
+    stamp(p, 0);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -217,6 +233,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0) stamp(p, 1);
 
   if (warp == 0 || warp == 2) {
     // ------------------------------ TMA producers -----------------------------
@@ -255,7 +272,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           } else {
 #pragma unroll
             for (int m = 0; m < MT; ++m)
-              tma_load_2d_hint(sw + kUmmaWTileBytes + m * kUmmaHTileBytes, &h_map, kb * kUmmaBK, m * 128,
+              tma_load_2d_hint(sw + w_tile_bytes + m * h_tile_bytes, &h_map, kb * kUmmaBK, m * 128,
                                &full_bar[st], pol);
           }
         }
@@ -291,11 +308,12 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             break;
           }
           tc_fence_after();
+          if (it == 0) stamp(p, 2);
           const uint32_t sw = smem_u32(smem + st * stage_bytes);
           const uint64_t bdesc = umma_smem_desc(sw);
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
-            const uint64_t adesc = umma_smem_desc(sw + kUmmaWTileBytes + m * kUmmaHTileBytes);
+            const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + m * h_tile_bytes));
             const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
 #pragma unroll
             for (int k = 0; k < kUmmaBK / 16; ++k) {
@@ -308,6 +326,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         }
         if (ok) umma_commit(&acc_full[j]);  // accumulator complete
       }
+      stamp(p, 3);
     }
   } else if (warp >= kUmmaEpiWarp0) {
     // -------------------------------- epilogue --------------------------------
@@ -345,6 +364,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       ++ta;
       if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
       tc_fence_after();
+      if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
       if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         for (int s = 0; s < S; ++s) {
@@ -434,6 +454,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[j]);
     }
+    if (ew == 0 && lane == 0) stamp(p, 5);
     // merge this thread's winners into the per-(row, draw) keys
     if (row_ok) {
       if (S == 1) {

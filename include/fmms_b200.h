@@ -110,6 +110,14 @@ int fmms_last_path(void);
  * bench harness (bench/triton_benchmark_lib.py:237-249). */
 int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream);
 
+/* Profiling aid: while `stamps_dev` (device memory, 8 x 8 bytes per persistent CTA, at least
+ * 320 CTAs) is set, every sampling kernel records %globaltimer at its phases for each CTA:
+ * [0] entry, [1] prologue done, [2] first operands landed, [3] last MMA issued, [4] last
+ * accumulator complete, [5] epilogue done, [6] CTA done, [7] winners decoded (last CTA only).
+ * Pass NULL to switch it off (the default).  Counterpart of the reference's Proton
+ * intra-kernel scopes (benchmarking/insert_proton_records.py). */
+int fmms_debug_stamps(unsigned long long* stamps_dev);
+
 /* Host-only: the launch plan fmms_sample would use on a device with `num_sms`
  * SMs and `max_smem_bytes` of opt-in shared memory per block; needs no GPU.
  * plan[0] = FMMS_PATH_*, [1] = persistent CTAs, [2] = vocabulary rows of the tallest tile
