@@ -20,7 +20,7 @@ namespace fmms {
 constexpr int kVersion = 1000;
 constexpr int kMaxParts = 320;      // upper bound on candidate rows in the workspace (2 per persistent CTA)
 constexpr int kMaxDevices = 16;
-constexpr int kGemvAutoMaxBatch = 3;  // auto-dispatch: batches up to this use the weight-streaming kernel (measured crossover)
+constexpr int kGemvAutoMaxBatch = 2;  // auto-dispatch: batches up to this use the weight-streaming kernel (measured crossover)
 
 static thread_local int g_last_path = FMMS_PATH_NONE;
 static unsigned long long* g_stamps = nullptr;  // see fmms_debug_stamps()
@@ -134,6 +134,46 @@ static size_t workspace_bytes_for(int B, int S) {
 }
 static size_t workspace_item_capacity(size_t bytes) { return (bytes - 256) / (8 * (1 + (size_t)kMaxParts)); }
 
+// [rows, cols] bf16 matrix seen as (inner columns, rows, cols / inner groups); box = inner x box_rows x groups.
+static int get_tensor_map_3d(const void* ptr, long long rows, long long cols, int inner, int box_rows, int slabs,
+                             CUtensorMapSwizzle swz, CUtensorMap* out) {
+  MapKey key{ptr, rows, cols, box_rows, inner + 1000 * slabs, (int)swz};
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (const MapEntry& e : g_maps)
+      if (e.key == key) {
+        *out = e.map;
+        return kOk;
+      }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return kErrCuda;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(cols / inner)};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)inner * 2};
+  cuuint32_t box[3] = {(cuuint32_t)inner, (cuuint32_t)box_rows, (cuuint32_t)slabs};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return kErrCuda;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_maps.size() >= 64) g_maps.erase(g_maps.begin());
+    g_maps.push_back(MapEntry{key, m});
+  }
+  *out = m;
+  return kOk;
+}
+static int get_tensor_map_slabs(const void* ptr, long long rows, long long cols, int box_rows, int slabs,
+                                CUtensorMap* out) {
+  return get_tensor_map_3d(ptr, rows, cols, 64, box_rows, slabs, CU_TENSOR_MAP_SWIZZLE_128B, out);
+}
+static int get_tensor_map_chunks(const void* ptr, long long rows, long long cols, int box_rows, int chunks,
+                                 CUtensorMap* out) {
+  return get_tensor_map_3d(ptr, rows, cols, 256, box_rows, chunks, CU_TENSOR_MAP_SWIZZLE_NONE, out);
+}
+
 // ---- GEMV launch ----------------------------------------------------------------
 template <int NB>
 static int launch_gemv_nb(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
@@ -174,10 +214,19 @@ static int umma_mt2_nt_cap() {
   return v;
 }
 
+static int gemv_chunks(int NB, int D) {
+  static const int forced = env_int("FMMS_GEMV_CHUNKS");
+  if (D % kGemvCols != 0 || D / kGemvCols < 2) return 1;  // the 3-D view needs whole chunks
+  if (forced == 1 || forced == 2) return forced;
+  return 2;  // 32-64 KiB per TMA operation (measured: B = 1 on the Qwen head 218 -> 183 us)
+}
+
 static int gemv_stages(const DeviceInfo& d, int NB, int D) {
-  // about 96-128 KiB of W in flight per SM: 6 x 16 KiB or 4 x 32 KiB stages
-  int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : (gemv_rows_per_warp(NB) == 8 ? 4 : kGemvMaxStages);
-  while (stages >= 3 && gemv_smem_bytes(NB, D, stages) > (size_t)d.max_smem_optin) --stages;
+  // about 96-128 KiB of W in flight per SM
+  const int ck = gemv_chunks(NB, D);
+  const int want = (int)(131072 / ((size_t)ck * gemv_stage_bytes(NB)));
+  int stages = gemv_stage_cap() >= 3 ? gemv_stage_cap() : (want < 3 ? 3 : (want > kGemvMaxStages ? kGemvMaxStages : want));
+  while (stages >= 3 && gemv_smem_bytes(NB, D, stages, ck) > (size_t)d.max_smem_optin) --stages;
   return stages >= 3 ? stages : 0;
 }
 
@@ -189,10 +238,15 @@ static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream
   CUtensorMap map;
   const int NB = p.B;
   const int kGemvRows = gemv_rows(NB);
-  int rc = get_tensor_map(W, p.V, p.D, kGemvRows, kGemvCols, CU_TENSOR_MAP_SWIZZLE_NONE, &map);
+  p.gemv_chunks = gemv_chunks(NB, p.D);
+  int rc;
+  if (p.gemv_chunks > 1)
+    rc = get_tensor_map_chunks(W, p.V, p.D, kGemvRows, p.gemv_chunks, &map);
+  else
+    rc = get_tensor_map(W, p.V, p.D, kGemvRows, kGemvCols, CU_TENSOR_MAP_SWIZZLE_NONE, &map);
   if (rc != kOk) return -rc;
   p.stages = gemv_stages(d, NB, p.D);
-  const size_t smem = gemv_smem_bytes(NB, p.D, p.stages);
+  const size_t smem = gemv_smem_bytes(NB, p.D, p.stages, p.gemv_chunks);
   const int groups = (p.V + kGemvRows - 1) / kGemvRows;
   const int grid = groups < d.num_sms ? groups : d.num_sms;
   switch (NB) {
@@ -221,22 +275,50 @@ static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wq, const CUtensorMa
     d.umma_attr[MT] = true;
   }
   umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.nt_cap, pl.units_total,
-                                                                     pl.q_units, pl.h_rows);
+                                                                     pl.q_units, pl.h_rows, pl.slabs);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
+static int umma_slabs_force() {
+  static const int v = env_int("FMMS_UMMA_SLABS");
+  return v;
+}
+
+static int build_umma_maps(const void* W, const void* H, const SampleParams& p, const UmmaPlan& pl,
+                           CUtensorMap* wq, CUtensorMap* wq1, CUtensorMap* hm) {
+  int rc;
+  if (pl.slabs > 1) {
+    rc = get_tensor_map_slabs(W, p.V, p.D, pl.q_units * 16, pl.slabs, wq);
+    if (rc != kOk) return rc;
+    *wq1 = *wq;
+    if (pl.q_units > 1) {
+      rc = get_tensor_map_slabs(W, p.V, p.D, (pl.q_units - 1) * 16, pl.slabs, wq1);
+      if (rc != kOk) return rc;
+    }
+    return get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.slabs, hm);
+  }
+  rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, wq);
+  if (rc != kOk) return rc;
+  *wq1 = *wq;  // a CTA only uses the lower box when some tile is one unit shorter
+  if (pl.q_units > 1) {
+    rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, wq1);
+    if (rc != kOk) return rc;
+  }
+  return get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, hm);
+}
+
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
-  const UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(), umma_min_tiles());
+  UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
+                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force());
   if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
   CUtensorMap wq, wq1, hm;
-  int rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wq);
-  if (rc != kOk) return -rc;
-  wq1 = wq;  // a CTA only uses the lower box when some tile is one unit shorter
-  if (pl.q_units > 1) {
-    rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &wq1);
-    if (rc != kOk) return -rc;
+  int rc = build_umma_maps(W, H, p, pl, &wq, &wq1, &hm);
+  if (rc != kOk && pl.slabs > 1) {
+    // the driver refused the 3-D view: fall back to one slab per operation
+    pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(),
+                   umma_min_tiles(), 0, 0);
+    rc = build_umma_maps(W, H, p, pl, &wq, &wq1, &hm);
   }
-  rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &hm);
   if (rc != kOk) return -rc;
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * 16;
@@ -348,10 +430,10 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
     plan[3] = (groups + plan[1] - 1) / plan[1];
     plan[4] = gemv_stages(d, B, D);
     plan[5] = 1;
-    plan[6] = (int)gemv_smem_bytes(B, D, plan[4]);
+    plan[6] = (int)gemv_smem_bytes(B, D, plan[4], gemv_chunks(B, D));
     plan[7] = plan[1];
   } else {
-    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes);
+    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0);
     plan[0] = FMMS_PATH_MMA;
     plan[1] = pl.grid;
     plan[2] = pl.q_units * 16;

@@ -50,6 +50,7 @@ struct SampleParams {
   int* status_dev;
   unsigned long long* stamps;  // optional [gridDim.x][8] %globaltimer stamps of the kernel's phases (null = off)
   int stages;                // shared-memory ring depth
+  int gemv_chunks;           // weight-streaming kernel: 256-column chunks fetched per TMA operation
   int tile_rows;             // tensor-core path: vocabulary rows per tile
   int tiles_per_cta;         // tensor-core path
   // tensor parallelism (tp_world > 1): the last CTA also runs the cross-rank exchange
@@ -143,11 +144,14 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   }
 }
 
-__host__ __device__ inline int gemv_dpad(int D) { return (D + kGemvCols - 1) / kGemvCols * kGemvCols; }
+__host__ __device__ inline int gemv_dpad(int D, int chunks) {
+  const int w = kGemvCols * chunks;
+  return (D + w - 1) / w * w;
+}
 
-__host__ __device__ inline size_t gemv_smem_bytes(int NB, int D, int stages) {
-  return (size_t)stages * gemv_stage_bytes(NB) + (size_t)NB * gemv_dpad(D) * 2 + 16 * (size_t)stages +
-         kGemvConsumerWarps * 32 * 8 + 16;
+__host__ __device__ inline size_t gemv_smem_bytes(int NB, int D, int stages, int chunks) {
+  return (size_t)stages * chunks * gemv_stage_bytes(NB) + (size_t)NB * gemv_dpad(D, chunks) * 2 +
+         16 * (size_t)stages + kGemvConsumerWarps * 32 * 8 + 16;
 }
 
 __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t x) {
@@ -160,13 +164,15 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int kGemvRowsPerWarp = gemv_rows_per_warp(NB);
   constexpr int kGemvRows = gemv_rows(NB);
-  constexpr int kGemvStageBytes = gemv_stage_bytes(NB);
+  constexpr int kChunkBytes = gemv_stage_bytes(NB);  // one rows x 256-column chunk
+  const int CK = p.gemv_chunks;                      // chunks per stage (CK > 1: the map is 3-D)
+  const int kGemvStageBytes = CK * kChunkBytes;
   constexpr int kRowShift = (kGemvRowsPerWarp == 8) ? 3 : 2;
   // (row, b, s) results a lane may own: rows_per_warp * NB * S <= rows_per_warp * 32
   constexpr int kGemvItemsPerLane = kGemvRowsPerWarp;
   const int stages = p.stages;
-  const int KC = (p.D + kGemvCols - 1) / kGemvCols;
-  const int Dpad = KC * kGemvCols;
+  const int KC = ((p.D + kGemvCols - 1) / kGemvCols + CK - 1) / CK;  // pipeline steps per row group
+  const int Dpad = KC * CK * kGemvCols;
 
   uint8_t* w_tiles = smem;
   __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(smem + (size_t)stages * kGemvStageBytes);
@@ -220,8 +226,12 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
           const uint32_t n = (uint32_t)(it / stages);
           if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) break;
           mbar_arrive_expect_tx(&full_bar[st], kGemvStageBytes);
-          tma_load_2d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, kc * kGemvCols,
-                           g * kGemvRows, &full_bar[st], pol);
+          if (CK == 1)
+            tma_load_2d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, kc * kGemvCols, g * kGemvRows,
+                             &full_bar[st], pol);
+          else
+            tma_load_3d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, 0, g * kGemvRows, kc * CK,
+                             &full_bar[st], pol);
         }
         if (*abort_flag) break;
       }
@@ -267,29 +277,31 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
       const uint32_t n = (uint32_t)(it / stages);
       mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev);
 
-      float2 hreg[NB][4];
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        const uint4 hv = *reinterpret_cast<const uint4*>(hs + (size_t)b * Dpad + kc * kGemvCols + lane * 8);
-        hreg[b][0] = bf16x2_to_float2(hv.x);
-        hreg[b][1] = bf16x2_to_float2(hv.y);
-        hreg[b][2] = bf16x2_to_float2(hv.z);
-        hreg[b][3] = bf16x2_to_float2(hv.w);
-      }
-      const uint8_t* tile = w_tiles + (size_t)st * kGemvStageBytes + (size_t)(warp * kGemvRowsPerWarp) * (kGemvCols * 2) + lane * 16;
-#pragma unroll
-      for (int r = 0; r < kGemvRowsPerWarp; ++r) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * (kGemvCols * 2));
-        const float2 w0 = bf16x2_to_float2(wv.x), w1 = bf16x2_to_float2(wv.y);
-        const float2 w2 = bf16x2_to_float2(wv.z), w3 = bf16x2_to_float2(wv.w);
+      for (int c = 0; c < CK; ++c) {
+        float2 hreg[NB][4];
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          float2 a = acc[r][b];
-          a = __ffma2_rn(w0, hreg[b][0], a);
-          a = __ffma2_rn(w1, hreg[b][1], a);
-          a = __ffma2_rn(w2, hreg[b][2], a);
-          a = __ffma2_rn(w3, hreg[b][3], a);
-          acc[r][b] = a;
+          const uint4 hv = *reinterpret_cast<const uint4*>(hs + (size_t)b * Dpad + (kc * CK + c) * kGemvCols + lane * 8);
+          hreg[b][0] = bf16x2_to_float2(hv.x);
+          hreg[b][1] = bf16x2_to_float2(hv.y);
+          hreg[b][2] = bf16x2_to_float2(hv.z);
+          hreg[b][3] = bf16x2_to_float2(hv.w);
+        }
+        const uint8_t* tile = w_tiles + (size_t)st * kGemvStageBytes + (size_t)c * kChunkBytes + (size_t)(warp * kGemvRowsPerWarp) * (kGemvCols * 2) + lane * 16;
+#pragma unroll
+        for (int r = 0; r < kGemvRowsPerWarp; ++r) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * (kGemvCols * 2));
+          const float2 w0 = bf16x2_to_float2(wv.x), w1 = bf16x2_to_float2(wv.y);
+          const float2 w2 = bf16x2_to_float2(wv.z), w3 = bf16x2_to_float2(wv.w);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float2 a = acc[r][b];
+            a = __ffma2_rn(w0, hreg[b][0], a);
+            a = __ffma2_rn(w1, hreg[b][1], a);
+            a = __ffma2_rn(w2, hreg[b][2], a);
+            a = __ffma2_rn(w3, hreg[b][3], a);
+            acc[r][b] = a;
+          }
         }
       }
       __syncwarp();

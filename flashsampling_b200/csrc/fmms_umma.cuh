@@ -42,6 +42,7 @@ struct UmmaPlan {
   int stages;         // shared-memory ring depth
   int h_rows;         // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
   int mt;             // M tiles (1 or 2)
+  int slabs;          // 64-column K slabs per pipeline stage (one TMA operation fetches them all)
   size_t smem;
 };
 
@@ -49,8 +50,8 @@ struct UmmaPlan {
 // h_rows x 128 B)][16 KiB slack].  With fewer than 128 hidden-state rows the MMA's 128-row A
 // operand runs past its tile into whatever follows (the next stage, or the slack after the last
 // one); those accumulator lanes belong to no batch row and are never read.
-__host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows) {
-  return (size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128;
+__host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows, int slabs) {
+  return (size_t)slabs * ((size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128);
 }
 
 // Work split.  The vocabulary is dealt out in units of 16 rows: CTA c gets a contiguous range
@@ -58,7 +59,7 @@ __host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_ro
 // T near-equal tiles, so no CTA walks more than 16 rows beyond the average.  All tiles of all
 // CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
-                                   int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1) {
+                                   int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1, int D = 0, int slabs_force = 0) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
@@ -77,8 +78,23 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   if (pl.tiles_per_cta < min_tiles && u_max >= 4 * min_tiles) pl.tiles_per_cta = min_tiles;
   pl.q_units = (u_max + pl.tiles_per_cta - 1) / pl.tiles_per_cta;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
+  // One thread sustains only about three TMA operations per microsecond, so short tiles fetch
+  // several 64-column slabs of the hidden dimension per operation (a 3-D box), aiming at >= 40 KiB
+  // of W per operation (measured: 52 KiB operations stream the Qwen head 4% faster than 26 KiB ones).  Needs D % 64 == 0 (a slab index must not run into the next row).
+  pl.slabs = 1;
   const size_t fixed = 1024 /*barriers*/ + 1024 /*alignment*/ + kUmmaHTileMax /*A-operand overrun*/;
-  const size_t sb = umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows);
+  if (D > 0 && D % 64 == 0) {
+    const int w_slab = pl.q_units * 16 * 128;
+    int sk = slabs_force > 0 ? slabs_force : (40 * 1024 + w_slab - 1) / w_slab;
+    if (sk > 4) sk = 4;
+    if (sk > D / 64) sk = D / 64;
+    if (sk < 1) sk = 1;
+    // keep at least three stages in the ring
+    const int min_stages = (stages_cap == 2) ? 2 : 3;
+    while (sk > 1 && min_stages * umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, sk) + fixed > (size_t)max_smem) --sk;
+    pl.slabs = sk;
+  }
+  const size_t sb = umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, pl.slabs);
   int stages = stages_cap > 1 ? stages_cap : kUmmaMaxStages;
   if (stages > kUmmaMaxStages) stages = kUmmaMaxStages;
   while (stages > 2 && stages * sb + fixed > (size_t)max_smem) --stages;
@@ -180,12 +196,14 @@ template <int MT>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
                    const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
-                   const int units_total, const int q_units, const int h_rows) {
+                   const int units_total, const int q_units, const int h_rows, const int SK) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
-  const size_t w_tile_bytes = (size_t)q_units * 16 * 128, h_tile_bytes = (size_t)h_rows * 128;
+  // stage = [SK W slabs][MT x SK hidden-state slabs]; SK > 1 means the maps are 3-D (slab = dim 2)
+  const size_t w_slab_bytes = (size_t)q_units * 16 * 128, h_slab_bytes = (size_t)h_rows * 128;
+  const size_t w_tile_bytes = SK * w_slab_bytes, h_tile_bytes = SK * h_slab_bytes;
   const size_t stage_bytes = w_tile_bytes + MT * h_tile_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
   smem += 1024;  // stages start 1 KiB-aligned behind the barriers
@@ -197,7 +215,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int acc_stages = kTmemCols / (MT * nt_cap);
-  const int KB = (p.D + kUmmaBK - 1) / kUmmaBK;
+  const int KB = ((p.D + kUmmaBK - 1) / kUmmaBK + SK - 1) / SK;  // pipeline steps per tile
 
   const int cta = blockIdx.x;
 
@@ -256,7 +274,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         int v0, NT;
         walk.next(v0, NT);
         if (NT == 0) continue;
-        const uint32_t tx = is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u;
+        const uint32_t tx = (uint32_t)SK * (is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u);
         const CUtensorMap* wm = (NT == q_units * 16) ? &w_map_q : &w_map_q1;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int st = it % stages;
@@ -268,12 +286,15 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           uint8_t* sw = smem + st * stage_bytes;
           mbar_arrive_expect_tx(&full_bar[st], tx);
           if (is_w) {
-            tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
+            if (SK == 1) tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
+            else tma_load_3d_hint(sw, wm, 0, v0, kb * SK, &full_bar[st], pol);
           } else {
 #pragma unroll
-            for (int m = 0; m < MT; ++m)
-              tma_load_2d_hint(sw + w_tile_bytes + m * h_tile_bytes, &h_map, kb * kUmmaBK, m * 128,
-                               &full_bar[st], pol);
+            for (int m = 0; m < MT; ++m) {
+              uint8_t* dst = sw + w_tile_bytes + m * h_tile_bytes;
+              if (SK == 1) tma_load_2d_hint(dst, &h_map, kb * kUmmaBK, m * 128, &full_bar[st], pol);
+              else tma_load_3d_hint(dst, &h_map, 0, m * 128, kb * SK, &full_bar[st], pol);
+            }
           }
         }
       }
@@ -310,16 +331,19 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           tc_fence_after();
           if (it == 0) stamp(p, 2);
           const uint32_t sw = smem_u32(smem + st * stage_bytes);
-          const uint64_t bdesc = umma_smem_desc(sw);
+          for (int sl = 0; sl < SK; ++sl) {
+            // TMA packs the slabs of a box back to back: the slab pitch follows the tile height
+            const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)(sl * NT * 128));
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + m * h_tile_bytes));
-            const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
+            for (int m = 0; m < MT; ++m) {
+              const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + m * h_tile_bytes + sl * h_slab_bytes));
+              const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
 #pragma unroll
-            for (int k = 0; k < kUmmaBK / 16; ++k) {
-              // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
-              umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                        (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < kUmmaBK / 16; ++k) {
+                // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
+                umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                          (kb | sl | k) != 0 ? 1u : 0u);
+              }
             }
           }
           umma_commit(&empty_bar[st]);  // stage reusable once these MMAs have read it
