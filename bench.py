@@ -187,12 +187,24 @@ def run_b200(args):
     tp = TPInfo(rank=rank, size=world)
     wl = WORKLOADS[args.workload]
     V, D, S = wl["V"], wl["D"], wl["S"]
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    # multi-GPU steps are short: a longer sweep keeps the host's launches ahead of the GPU
+    flush = torch.empty((256 << 20) * (3 if world > 1 else 1), dtype=torch.uint8, device=device)
 
     from flashsampling_b200 import _lib as _fl
 
+    align = torch.zeros(1, device=device)
+
     def sweep_read():
         _fl.load().fmms_l2_sweep(flush.data_ptr(), flush.numel(), torch.cuda.current_stream().cuda_stream)
+        if world > 1:
+            # device-side alignment of the ranks right before the start event (enqueued, no host sync),
+            # as the reference's harness does, so that a step does not time another rank's lateness
+            dist.all_reduce(align)
+
+    def write_flush():
+        flush.zero_()
+        if world > 1:
+            dist.all_reduce(align)
 
     def barrier():
         if world > 1:
@@ -224,7 +236,7 @@ def run_b200(args):
         with ClockSampler(local_rank) as clk:
             times, wall = time_steps(step, steps, warmup, sweep_read, barrier)
         times = reduce_max(times)
-        ref_times, _ = time_steps(step, max(10, steps // 2), 3, flush.zero_, barrier)
+        ref_times, _ = time_steps(step, max(10, steps // 2), 3, write_flush, barrier)
         ref_times = reduce_max(ref_times)
         res = dict(B=B, path=path, times_ms=times, ref_times_ms=ref_times, wall_s=wall, clocks=clk.summary(),
                    n_copies=n_copies)

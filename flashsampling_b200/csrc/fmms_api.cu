@@ -514,10 +514,8 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
     for (int r = 0; r < tpa->world; ++r) {
       if (!tpa->peer_buffers[r]) return FMMS_ERR_BAD_ARG;
       p.tp_peers.slots[r] = reinterpret_cast<TpRecord*>(tpa->peer_buffers[r]);
-      p.tp_peers.flags[r] = reinterpret_cast<unsigned int*>(
-          reinterpret_cast<unsigned char*>(tpa->peer_buffers[r]) +
-          (size_t)2 * tpa->world * tpa->max_items * sizeof(TpRecord));
     }
+    if (v_global_offset + (long long)V_local > 0xffffffffll) return FMMS_ERR_UNSUPPORTED;  // ids travel as 32 bits
   }
   p.status_dev = status_dev;
   p.stamps = g_stamps;
@@ -628,8 +626,6 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
   for (int r = 0; r < world; ++r) {
     if (!peer_buffers[r]) return FMMS_ERR_BAD_ARG;
     peers.slots[r] = reinterpret_cast<TpRecord*>(peer_buffers[r]);
-    peers.flags[r] = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(peer_buffers[r]) +
-                                                     (size_t)2 * world * max_items * sizeof(TpRecord));
   }
   const int threads = n_items >= 1024 ? 1024 : ((n_items + 31) / 32 * 32 < 32 ? 32 : (n_items + 31) / 32 * 32);
   tp_exchange_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(

@@ -69,9 +69,11 @@ __device__ __forceinline__ void stamp(const SampleParams& p, int slot) {
 
 template <class SyncFn>
 __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, int nthreads, SyncFn sync,
-                                              volatile int* is_last) {
-  __threadfence();
-  sync();
+                                              volatile int* is_last, bool fenced_and_synced = false) {
+  if (!fenced_and_synced) {
+    __threadfence();
+    sync();
+  }
   if (tid == 0) *is_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
   sync();
   if (tid == 0) stamp(p, 6);
@@ -93,55 +95,32 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
     return;
   }
   // Tensor parallel: this rank's winners go straight into every rank's exchange buffer (see
-  // fmms_tp.cuh for the protocol), then the same CTA waits for the peers and picks the maximum.
+  // fmms_tp.cuh for the protocol), then the same threads wait for the peers' records and keep
+  // the maximum.  Items are processed in rounds of `nthreads`: send a round, then receive it.
   const int world = p.tp_world, rank = p.tp_rank;
   const int parity = (int)(p.tp_epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * p.tp_max_items;
+  const TpRecord* mine = p.tp_peers.slots[rank] + (size_t)parity * world * p.tp_max_items;
   for (int item = tid; item < n; item += nthreads) {
     const unsigned long long k = atomicExch(&p.keys[item], 0ull);
     float v;
     int idx;
     cand_key_decode(k, v, idx);
-    const long long gid = p.v_offset + idx;
-    const int4 rec = make_int4(__float_as_int(v), 0, (int)(unsigned int)(unsigned long long)gid,
-                               (int)(unsigned int)((unsigned long long)gid >> 32));
-    for (int q = 0; q < world; ++q) *reinterpret_cast<int4*>(p.tp_peers.slots[q] + my_row + item) = rec;
+    tp_send(p.tp_peers, world, my_row + item, v, p.v_offset + idx, p.tp_epoch);
   }
   if (tid == 0) *p.ticket = 0u;
-  __threadfence_system();
-  sync();
-  if (tid < world) st_release_sys(p.tp_peers.flags[tid] + (size_t)rank * kTpFlagStride, p.tp_epoch);
-  if (tid == 0) *is_last = 1;  // reused below: 1 = all peers arrived, 2 = timed out
-  sync();
-  if (tid < world) {
-    const unsigned int* f = p.tp_peers.flags[rank] + (size_t)tid * kTpFlagStride;
-    const unsigned long long t0 = global_timer_ns();
-    unsigned int spins = 0;
-    while ((int)(ld_acquire_sys(f) - p.tp_epoch) < 0) {
-      if ((++spins & 0xffu) == 0 && global_timer_ns() - t0 > p.tp_wait_ns) {
-        *is_last = 2;
-        if (p.status_dev) atomicExch(p.status_dev, kErrTimeout);
-        break;
-      }
-    }
-  }
-  sync();
-  const bool timed_out = (*is_last == 2);
-  const TpRecord* mine = p.tp_peers.slots[rank] + (size_t)parity * world * p.tp_max_items;
   for (int item = tid; item < n; item += nthreads) {
-    float bv = -INFINITY;
-    long long bi = 0x7fffffffffffffffll;
-    for (int r = 0; r < world; ++r) {
-      const TpRecord rec = ld_record_volatile(mine + (size_t)r * p.tp_max_items + item);
-      if (rec.val > bv || (rec.val == bv && rec.idx < bi)) {
-        bv = rec.val;
-        bi = rec.idx;
-      }
+    float bv;
+    long long bi;
+    if (!tp_recv_max(mine, world, p.tp_max_items, item, p.tp_epoch, p.tp_wait_ns, bv, bi)) {
+      if (p.status_dev) atomicExch(p.status_dev, kErrTimeout);
+      bi = -1;
     }
     const int s = item / p.B, b = item - s * p.B;
-    p.out_idx[(size_t)b * p.S + s] = timed_out ? -1 : bi;
+    p.out_idx[(size_t)b * p.S + s] = bi;
     if (p.out_val) p.out_val[(size_t)b * p.S + s] = bv;
   }
+  if (tid == 0) stamp(p, 7);
 }
 
 __host__ __device__ inline int gemv_dpad(int D, int chunks) {

@@ -1,15 +1,15 @@
 // Tensor-parallel exchange of per-row winners over NVLink peer memory.
 //
-// Every rank owns a symmetric buffer: `slots[2][world][max_items]` of 16-byte records
-// (fp32 value, int64 global id) followed by `flags[world]` (one 128-byte line each).
-// A step with epoch e uses slot parity e & 1.  Rank r writes its records into
-// slots[e & 1][r] of EVERY rank with plain 16-byte stores through peer pointers, then
-// release-stores e into flags[r] of every rank; it then waits (bounded) until all of its
-// own flags show e and takes the maximum over the `world` records of each item.  All loads
-// are local; the only traffic that crosses NVLink is 16 bytes per item per peer plus the
-// flags.  Epochs only grow, so flags are never reset, and the two parities keep a fast rank
-// from overwriting records a slow rank is still reading (a rank can be at most one step
-// ahead, because its own step e+1 cannot finish before every rank has signalled e+1).
+// Every rank owns a symmetric buffer `slots[2][world][max_items]` of 16-byte records.  A record
+// carries its own validity: {value bits, epoch, global id, epoch}, each half an 8-byte word that
+// NVLink delivers atomically, so no separate flag and no fence is needed (the "low-latency"
+// protocol of collective libraries).  In step `epoch` rank r stores its records into
+// slots[epoch & 1][r] of EVERY rank with plain peer stores and then reads its own buffer, spinning
+// (bounded) on each record until both halves show this epoch, and keeps the maximum over ranks.
+// All loads are local; 16 bytes per item and peer cross NVLink, once, one way.  Epochs only grow
+// (0 = never written), and the two parities keep a fast rank from overwriting records a slow rank
+// has not read yet: a rank cannot finish step e+1 before every rank has sent its step-e+1 records,
+// which each rank does only after reading all of step e.
 #pragma once
 
 #include "fmms_common.cuh"
@@ -17,40 +17,69 @@
 namespace fmms {
 
 constexpr int kTpMaxWorld = 8;
-constexpr int kTpFlagStride = 32;  // uint32 per flag line (128 bytes)
+constexpr int kTpFlagStride = 32;  // reserved tail of the buffer (kept for layout compatibility)
 
 struct TpRecord {
-  float val;
-  int pad;
-  long long idx;
+  unsigned int val_bits, epoch0, idx, epoch1;
 };
 static_assert(sizeof(TpRecord) == 16, "record must be one 16-byte store");
 
 struct TpPeers {
   TpRecord* slots[kTpMaxWorld];
-  unsigned int* flags[kTpMaxWorld];
 };
 
 __host__ __device__ inline size_t tp_buffer_bytes(int world, int max_items) {
   return (size_t)2 * world * max_items * sizeof(TpRecord) + (size_t)world * kTpFlagStride * 4;
 }
 
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_record(TpRecord* p, float v, unsigned int idx, unsigned int epoch) {
+  asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch),
+               "r"(idx), "r"(epoch)
+               : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ TpRecord ld_record_volatile(const TpRecord* p) {
+
+__device__ __forceinline__ TpRecord ld_record(const TpRecord* p) {
   TpRecord r;
-  int a, b, c, d;
-  asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(p) : "memory");
-  r.val = __int_as_float(a);
-  r.pad = b;
-  r.idx = (long long)(((unsigned long long)(unsigned int)d << 32) | (unsigned int)c);
+  asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.val_bits), "=r"(r.epoch0), "=r"(r.idx), "=r"(r.epoch1)
+               : "l"(p)
+               : "memory");
   return r;
+}
+
+// Send this rank's record of `item` to every rank.
+__device__ __forceinline__ void tp_send(const TpPeers& peers, int world, size_t row_item, float v, long long gid,
+                                        unsigned int epoch) {
+  for (int q = 0; q < world; ++q) st_record(peers.slots[q] + row_item, v, (unsigned int)gid, epoch);
+}
+
+// Wait (bounded) for all ranks' records of `item` in this rank's buffer and reduce them.
+// Returns false on time-out.
+__device__ __forceinline__ bool tp_recv_max(const TpRecord* mine, int world, int max_items, int item,
+                                            unsigned int epoch, unsigned long long wait_limit_ns, float& bv,
+                                            long long& bi) {
+  bv = -INFINITY;
+  bi = 0x7fffffffffffffffll;
+  unsigned long long t0 = 0;
+  for (int r = 0; r < world; ++r) {
+    const TpRecord* src = mine + (size_t)r * max_items + item;
+    TpRecord rec = ld_record(src);
+    unsigned int spins = 0;
+    while (rec.epoch0 != epoch || rec.epoch1 != epoch) {
+      if ((++spins & 0x3fu) == 0) {
+        if (t0 == 0) t0 = global_timer_ns();
+        else if (global_timer_ns() - t0 > wait_limit_ns) return false;
+      }
+      rec = ld_record(src);
+    }
+    const float v = __uint_as_float(rec.val_bits);
+    const long long id = (long long)rec.idx;
+    if (v > bv || (v == bv && id < bi)) {
+      bv = v;
+      bi = id;
+    }
+  }
+  return true;
 }
 
 // One CTA.  local_idx/local_val: this rank's winners [n_items] (item = b * S + s).
@@ -61,44 +90,15 @@ __global__ void tp_exchange_kernel(const long long* __restrict__ local_idx, cons
   const int tid = threadIdx.x;
   const int parity = (int)(epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * max_items;
-  for (int i = tid; i < n_items; i += blockDim.x) {
-    const float v = local_val[i];
-    const long long id = local_idx[i];
-    const int4 rec = make_int4(__float_as_int(v), 0, (int)(unsigned int)(unsigned long long)id,
-                               (int)(unsigned int)((unsigned long long)id >> 32));
-    for (int p = 0; p < world; ++p) *reinterpret_cast<int4*>(peers.slots[p] + my_row + i) = rec;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < world) st_release_sys(peers.flags[tid] + (size_t)rank * kTpFlagStride, epoch);
-  __shared__ int timed_out;
-  if (tid == 0) timed_out = 0;
-  __syncthreads();
-  if (tid < world) {
-    const unsigned int* f = peers.flags[rank] + (size_t)tid * kTpFlagStride;
-    const unsigned long long t0 = global_timer_ns();
-    unsigned int spins = 0;
-    while ((int)(ld_acquire_sys(f) - epoch) < 0) {
-      if ((++spins & 0xffu) == 0 && global_timer_ns() - t0 > wait_limit_ns) {
-        timed_out = 1;
-        if (status_dev) atomicExch(status_dev, kErrTimeout);
-        break;
-      }
-    }
-  }
-  __syncthreads();
   const TpRecord* mine = peers.slots[rank] + (size_t)parity * world * max_items;
+  for (int i = tid; i < n_items; i += blockDim.x) tp_send(peers, world, my_row + i, local_val[i], local_idx[i], epoch);
   for (int i = tid; i < n_items; i += blockDim.x) {
-    float bv = -INFINITY;
-    long long bi = 0x7fffffffffffffffll;
-    for (int r = 0; r < world; ++r) {
-      const TpRecord rec = ld_record_volatile(mine + (size_t)r * max_items + i);
-      if (rec.val > bv || (rec.val == bv && rec.idx < bi)) {
-        bv = rec.val;
-        bi = rec.idx;
-      }
+    float bv;
+    long long bi;
+    if (!tp_recv_max(mine, world, max_items, i, epoch, wait_limit_ns, bv, bi)) {
+      if (status_dev) atomicExch(status_dev, kErrTimeout);
+      bi = -1;  // never hand out an id computed from stale records
     }
-    if (timed_out) bi = -1;  // never hand out an id computed from stale records
     out_idx[i] = bi;
     if (out_val) out_val[i] = bv;
   }

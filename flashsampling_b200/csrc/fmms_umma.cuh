@@ -502,7 +502,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last);
+    finish_sample(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
   }
 }
 

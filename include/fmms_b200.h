@@ -131,9 +131,9 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
  *
  * Each rank samples its own block with fmms_sample() (v_global_offset = first global row of
  * the block, out_val requested) and then calls fmms_tp_exchange(): every rank writes its
- * per-row (value, id) winners into every rank's symmetric buffer with plain peer stores,
- * signals an epoch flag, waits (bounded) for the other ranks' flags and keeps the largest
- * value per row.  All ranks end with the same ids.  This replaces the symmetric-memory
+ * per-row (value, id, epoch) records into every rank's symmetric buffer with plain peer
+ * stores, waits (bounded) until the records of all ranks in its own buffer carry this
+ * step's epoch, and keeps the largest value per row (ids below 2^32).  All ranks end with the same ids.  This replaces the symmetric-memory
  * fan-out of per-tile candidates plus host-launched barrier and reduce of the reference:
  * allocate_symm_mem_outputs / tp_post_kernel_reduce (tensor_parallel_reduce.py:21-85) and
  * the in-kernel peer stores (core.py:614-632).
@@ -168,7 +168,7 @@ int fmms_tp_free(void* dev_ptr);
 /* The exchange step (one small kernel).  `peer_buffers[world]` are the device pointers of
  * every rank's buffer as seen from this process (own buffer at index `rank`); `epoch` must
  * be the same on all ranks and grow by one per step, starting at 1; `wait_limit_ns` bounds
- * the flag wait (0 = 2 s), after which FMMS_ERR_TIMEOUT is written to `status_dev` and the
+ * the wait for the peers' records (0 = 2 s), after which FMMS_ERR_TIMEOUT is written to `status_dev` and the
  * ids are set to -1.  Replaces symm_mem_hdl.barrier() + _local_reduce over world * tiles
  * (tensor_parallel_reduce.py:77-84). */
 int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_items, int max_items,
