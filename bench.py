@@ -326,7 +326,7 @@ def run_b200(args):
         "write_flush_protocol_note": "the reference's protocol: a 256 MB buffer is zeroed before each timed call; its "
                                      "dirty lines are written back during the timed kernel",
         "clocks": main["clocks"],
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
             "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"],
@@ -337,7 +337,7 @@ def run_b200(args):
             "peak_kind": f"of {peak_kind}", "traffic": traffic,
             "algorithmic_bytes_per_launch": algorithmic_bytes(v_local, D, B, S),
             "frac_of_8tbs": round(ach / 8000, 4),
-            "note": "duration = mean CUDA-event time of the call (sampling kernel + candidate reduction)",
+            "note": "duration = mean CUDA-event time of the call = one launch of the fused sampling kernel (launch latency included)",
         },
     }
     if sweep:
