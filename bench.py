@@ -53,6 +53,13 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["bf16_tflops"])
+    return 1590.0
+
+
 class ClockSampler:
     """Polls SM clock, power and throttle reasons of one GPU through NVML (read-only) from a
     background thread while the timed region runs; falls back to an empty summary without NVML."""
@@ -281,6 +288,7 @@ def run_b200(args):
             gbs = algorithmic_bytes(V, D, b, S) / (us * 1e-6) / 1e9
             sweep.append(dict(B=b, us=round(us, 2), path=r["path"], algo_gbs=round(gbs, 1),
                               frac_of_8tbs=round(gbs / 8000, 4), x_weight_read_at_8tbs=round(us / (2 * V * D / 8e12 * 1e6), 4),
+                              tflops=round(2.0 * V * D * b / (us * 1e-6) / 1e12, 1),
                               write_flush_us=round(statistics.median(r["ref_times_ms"]) * 1e3, 2)))
 
     if rank != 0:
@@ -292,6 +300,9 @@ def run_b200(args):
     mean_ms = statistics.fmean(main["times_ms"])
     peak, peak_kind = measured_peaks()
     ach = algorithmic_bytes(v_local, D, B, S) / (mean_ms * 1e-3) / 1e9
+    flops = 2.0 * v_local * D * B
+    tflops_peak = measured_tensor_peak()
+    tensor_bound = flops / (tflops_peak * 1e12) > algorithmic_bytes(v_local, D, B, S) / (peak * 1e9)
     traffic = None
     tfile = ROOT / "profiles" / "traffic.json"
     if tfile.exists():
@@ -332,13 +343,19 @@ def run_b200(args):
             "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"],
             "note": "pinned host hidden states + temperature -> device, sample, ids -> host; wall clock per step",
         },
-        "roofline": {
+        "roofline": ({
+            "bound": "tensor", "achieved": round(flops / (mean_ms * 1e-3) / 1e12, 1), "peak": tflops_peak,
+            "unit": "TFLOP/s", "frac": round(flops / (mean_ms * 1e-3) / 1e12 / tflops_peak, 4),
+            "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)", "traffic": traffic,
+            "algorithmic_flops_per_launch": flops, "hbm_gbs": round(ach, 1),
+            "note": "above ~200 batch rows the 2*V*d*B flops take longer than the weight stream",
+        } if tensor_bound else {
             "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
             "peak_kind": f"of {peak_kind}", "traffic": traffic,
             "algorithmic_bytes_per_launch": algorithmic_bytes(v_local, D, B, S),
             "frac_of_8tbs": round(ach / 8000, 4),
             "note": "duration = mean CUDA-event time of the call = one launch of the fused sampling kernel (launch latency included)",
-        },
+        }),
     }
     if sweep:
         line["sweep"] = sweep

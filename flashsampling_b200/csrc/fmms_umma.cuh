@@ -191,6 +191,83 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- epilogue scan shared by the tensor-core kernels ---------------------------------------
+struct EpiRow {
+  int b;          // batch row this thread owns
+  bool row_ok;    // b < B
+  bool greedy, ext, ret_logits, quad_aligned;
+  float inv_t;
+};
+
+// Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
+// quadrant, first column of the tile) for draw `s`: scale, add noise, keep the running (max, id)
+// of the thread's row.  The tile's first column is vocabulary row v0 of this shard.
+__device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
+                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
+  for (int c = c_begin; c < c_end; c += 32) {
+    uint32_t acc[32];
+    tmem_ld32(t_addr + (uint32_t)c, acc);
+    if (e.row_ok) {
+      const int vbase = v0 + c;
+      if (e.ret_logits && s == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c + i < c_end && vbase + i < p.V)
+            p.logits_out[(size_t)e.b * p.V + vbase + i] = __uint_as_float(acc[i]);
+      }
+      if (e.greedy) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float y = __uint_as_float(acc[i]);
+          if (c + i < c_end && vbase + i < p.V && y > bv) {
+            bv = y;
+            bi = vbase + i;
+          }
+        }
+      } else if (e.ext) {
+        const float* nz = p.ext_noise + ((size_t)s * p.B + e.b) * p.noise_ld + vbase;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (c + i < c_end && vbase + i < p.V) {
+            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, nz[i]);
+            if (y > bv) {
+              bv = y;
+              bi = vbase + i;
+            }
+          }
+        }
+      } else if (e.quad_aligned) {
+        const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint4 q = noise_block(p.seed, s, e.b, q0 + g);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            const int i = g * 4 + wi;
+            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
+            if (c + i < c_end && vbase + i < p.V && y > bv) {
+              bv = y;
+              bi = vbase + i;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
+          const uint4 q = noise_block(p.seed, s, e.b, vg >> 2);
+          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+          if (c + i < c_end && vbase + i < p.V && y > bv) {
+            bv = y;
+            bi = vbase + i;
+          }
+        }
+      }
+    }
+  }
+}
+
 // ---- the kernel ------------------------------------------------------------------
 template <int MT>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
@@ -368,6 +445,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     const bool quad_aligned = (p.v_offset & 3) == 0;
     float invT = 1.0f;
     if (row_ok && !greedy) invT = 1.0f / p.temperature[(size_t)b * p.temp_stride];
+    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT};
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * 2 + wg) * ((size_t)S * p.B);
 
@@ -398,68 +476,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          for (int c = c_begin; c < c_end; c += 32) {
-            uint32_t acc[32];
-            tmem_ld32(t_addr + (uint32_t)c, acc);
-            if (row_ok) {
-              const int vbase = v0 + c;
-              if (ret_logits && s == 0) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (c + i < c_end && vbase + i < p.V)
-                    p.logits_out[(size_t)b * p.V + vbase + i] = __uint_as_float(acc[i]);
-              }
-              if (greedy) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  const float y = __uint_as_float(acc[i]);
-                  if (c + i < c_end && vbase + i < p.V && y > bv) {
-                    bv = y;
-                    bi = vbase + i;
-                  }
-                }
-              } else if (ext) {
-                const float* nz = p.ext_noise + ((size_t)s * p.B + b) * p.noise_ld + vbase;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  if (c + i < c_end && vbase + i < p.V) {
-                    const float y = fmaf(__uint_as_float(acc[i]), invT, nz[i]);
-                    if (y > bv) {
-                      bv = y;
-                      bi = vbase + i;
-                    }
-                  }
-                }
-              } else if (quad_aligned) {
-                const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                  const uint4 q = noise_block(p.seed, s, b, q0 + g);
-                  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const int i = g * 4 + e;
-                    const float y = fmaf(__uint_as_float(acc[i]), invT, gumbel_from_bits(w[e]));
-                    if (c + i < c_end && vbase + i < p.V && y > bv) {
-                      bv = y;
-                      bi = vbase + i;
-                    }
-                  }
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
-                  const uint4 q = noise_block(p.seed, s, b, vg >> 2);
-                  const float y = fmaf(__uint_as_float(acc[i]), invT, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
-                  if (c + i < c_end && vbase + i < p.V && y > bv) {
-                    bv = y;
-                    bi = vbase + i;
-                  }
-                }
-              }
-            }
-          }
+          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.B + b;
