@@ -177,7 +177,7 @@ def fused_mm_sample(
         exchange = get_exchange(tp, dev)
         v_begin = exchange.vocab_offset(V)
     out = torch.empty((B, num_samples), dtype=torch.int64, device=dev)
-    need_vals = return_values or (tp.size > 1 and not getattr(exchange, "fused", False))
+    need_vals = return_values or tp.size > 1
     vals = torch.empty((B, num_samples), dtype=torch.float32, device=dev) if need_vals else None
 
     stream = torch.cuda.current_stream(dev)
@@ -194,7 +194,7 @@ def fused_mm_sample(
         status.data_ptr(), stream.cuda_stream,
     )
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
-        and not two_stage
+        and not two_stage and B <= 256  # larger batches run as several launches, then one exchange
     with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
         if fused_tp:
             # one launch: the sampling kernel's last CTA runs the NVLink exchange itself

@@ -443,7 +443,7 @@ int fmms_num_sms(int* num_sms) {
 
 int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes) {
   if (!bytes || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
-  *bytes = workspace_bytes_for(B, S);
+  *bytes = workspace_bytes_for(B > 256 ? 256 : B, S);
   return FMMS_OK;
 }
 
@@ -501,6 +501,15 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
   return FMMS_OK;
 }
 
+constexpr int kMaxBatchPerLaunch = 256;
+
+struct TpArgs;
+static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                       int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                       int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
+                       float* logits_out, long long* out_idx, float* out_val, void* workspace,
+                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa);
+
 struct TpArgs {
   int rank, world, max_items;
   void* const* peer_buffers;
@@ -523,7 +532,35 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
   if ((flags & FMMS_FLAG_FORCE_GEMV) && (flags & FMMS_FLAG_FORCE_MMA)) return FMMS_ERR_BAD_ARG;
   if (v_global_offset < 0) return FMMS_ERR_BAD_ARG;
   if (D % 8 != 0 || ((uintptr_t)W_bf16 & 15) || ((uintptr_t)H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
-  if (B > 256) return FMMS_ERR_UNSUPPORTED;
+  if (B > kMaxBatchPerLaunch) {
+    // Larger batches run as consecutive launches over blocks of 256 rows (each streams W again,
+    // as the reference's 64-row tiles do); the noise stays keyed by the caller's row numbers.
+    if (tpa) return FMMS_ERR_UNSUPPORTED;
+    for (int b0 = 0; b0 < B; b0 += kMaxBatchPerLaunch) {
+      const int nb = B - b0 < kMaxBatchPerLaunch ? B - b0 : kMaxBatchPerLaunch;
+      const int rc = sample_rows(W_bf16, reinterpret_cast<const __nv_bfloat16*>(H_bf16) + (size_t)b0 * D,
+                                 temperature ? temperature + (size_t)b0 * temp_stride : nullptr, temp_stride, V_local,
+                                 D, nb, S, seed, v_global_offset, flags,
+                                 ext_noise ? ext_noise + (size_t)b0 * noise_ld : nullptr, noise_ld,
+                                 (long long)B * noise_ld, b0, logits_out ? logits_out + (size_t)b0 * V_local : nullptr,
+                                 out_idx + (size_t)b0 * S, out_val ? out_val + (size_t)b0 * S : nullptr, workspace,
+                                 workspace_bytes, status_dev, stream_v, nullptr);
+      if (rc != FMMS_OK) return rc;
+    }
+    return FMMS_OK;
+  }
+  return sample_rows(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
+                     ext_noise, noise_ld, (long long)B * noise_ld, 0, logits_out, out_idx, out_val, workspace,
+                     workspace_bytes, status_dev, stream_v, tpa);
+}
+
+static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                       int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                       int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
+                       float* logits_out, long long* out_idx, float* out_val, void* workspace,
+                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa) {
+  const bool greedy = flags & FMMS_FLAG_GREEDY;
+  (void)greedy;
   size_t need = 0;
   fmms_query_workspace(V_local, D, B, S, &need);
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return FMMS_ERR_WORKSPACE;
@@ -547,6 +584,8 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
   p.flags = flags;
   p.ext_noise = ext_noise;
   p.noise_ld = noise_ld;
+  p.noise_s_stride = noise_s_stride;
+  p.b_offset = b_offset;
   p.logits_out = logits_out;
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   const size_t cap = workspace_item_capacity(workspace_bytes);

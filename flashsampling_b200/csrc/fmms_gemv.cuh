@@ -38,8 +38,10 @@ struct SampleParams {
   unsigned long long seed;
   long long v_offset;        // global vocabulary id of row 0
   int flags;
-  const float* ext_noise;    // [S, B, noise_ld]
+  const float* ext_noise;    // element (s, b, v) at s * noise_s_stride + b * noise_ld + v
   long long noise_ld;
+  long long noise_s_stride;
+  int b_offset;              // batch row of this call's row 0 inside the caller's batch (keys the noise)
   float* logits_out;         // [B, V]
   unsigned long long* keys;  // [S * B] packed winners, zero on entry and on exit (atomicMax target)
   unsigned int* ticket;      // CTAs-done counter, zero on entry and on exit
@@ -321,10 +323,10 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
         } else {
           const float inv_t = 1.0f / p.temperature[(size_t)item_b * p.temp_stride];
           if (ext) {
-            y = fmaf(val, inv_t, p.ext_noise[((size_t)item_s * p.B + item_b) * p.noise_ld + v]);
+            y = fmaf(val, inv_t, p.ext_noise[(size_t)item_s * p.noise_s_stride + (size_t)item_b * p.noise_ld + v]);
           } else {
             const unsigned long long vg = (unsigned long long)(p.v_offset + v);
-            const uint4 q = noise_block(p.seed, item_s, item_b, vg >> 2);
+            const uint4 q = noise_block(p.seed, item_s, item_b + p.b_offset, vg >> 2);
             y = fmaf(val, inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
           }
         }

@@ -225,7 +225,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
           }
         }
       } else if (e.ext) {
-        const float* nz = p.ext_noise + ((size_t)s * p.B + e.b) * p.noise_ld + vbase;
+        const float* nz = p.ext_noise + (size_t)s * p.noise_s_stride + (size_t)e.b * p.noise_ld + vbase;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (c + i < c_end && vbase + i < p.V) {
@@ -240,7 +240,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
         const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const uint4 q = noise_block(p.seed, s, e.b, q0 + g);
+          const uint4 q = noise_block(p.seed, s, e.b + p.b_offset, q0 + g);
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {
@@ -256,7 +256,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
-          const uint4 q = noise_block(p.seed, s, e.b, vg >> 2);
+          const uint4 q = noise_block(p.seed, s, e.b + p.b_offset, vg >> 2);
           const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
           if (c + i < c_end && vbase + i < p.V && y > bv) {
             bv = y;

@@ -77,7 +77,8 @@ int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes);
  * core.py:480-635 plus stage-2 _local_reduce core.py:359-370).
  *
  *   W_bf16        [V_local, D] bf16 row-major, 16-byte aligned, D % 8 == 0
- *   H_bf16        [B, D] bf16 row-major, 16-byte aligned
+ *   H_bf16        [B, D] bf16 row-major, 16-byte aligned; more than 256 rows run as
+ *                 consecutive launches over blocks of 256 rows
  *   temperature   fp32; temp_stride 0 = one value for all rows (the
  *                 reference's 0-d tensor, core.py:228,513), 1 = one per row
  *   S             draws per row (num_samples)

@@ -96,6 +96,7 @@ MMA_SHAPES = [
     (100, 16, 1, 1), (129, 72, 2, 3), (1000, 256, 15, 2), (4097, 520, 16, 1), (5000, 1024, 17, 1),
     (6151, 264, 63, 2), (3000, 64, 64, 1), (2049, 128, 65, 1), (33, 8, 128, 1), (4500, 200, 129, 2),
     (9000, 512, 256, 1), (70000, 320, 33, 1), (50000, 4096, 8, 1),
+    (3000, 64, 300, 2), (2000, 128, 513, 1),  # more than 256 rows: consecutive launches over blocks of 256 rows
     (40000, 512, 256, 1), (70000, 320, 200, 2),  # CTA-pair kernel (cta_group::2): more than 128 rows, large vocabulary
     (18992, 4096, 64, 1), (16032, 2048, 8, 1), (18992, 1024, 130, 1),  # shard-sized: tiles of two heights, several K slabs per stage
 ]
