@@ -321,13 +321,15 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
         if (greedy) {
           y = val;
         } else {
-          const float inv_t = 1.0f / p.temperature[(size_t)item_b * p.temp_stride];
-          if (ext) {
-            y = fmaf(val, inv_t, p.ext_noise[(size_t)item_s * p.noise_s_stride + (size_t)item_b * p.noise_ld + v]);
+          const float temp = p.temperature[(size_t)item_b * p.temp_stride];
+          if (temp <= 0.f) {
+            y = val;  // temperature <= 0 selects greedy decoding for this row
+          } else if (ext) {
+            y = fmaf(val, 1.0f / temp, p.ext_noise[(size_t)item_s * p.noise_s_stride + (size_t)item_b * p.noise_ld + v]);
           } else {
             const unsigned long long vg = (unsigned long long)(p.v_offset + v);
             const uint4 q = noise_block(p.seed, item_s, item_b + p.b_offset, vg >> 2);
-            y = fmaf(val, inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+            y = fmaf(val, 1.0f / temp, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
           }
         }
         if (y > best_val[j]) {

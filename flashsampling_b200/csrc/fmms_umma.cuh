@@ -197,6 +197,7 @@ struct EpiRow {
   bool row_ok;    // b < B
   bool greedy, ext, ret_logits, quad_aligned;
   float inv_t;
+  bool noisy;     // false for a row whose temperature is <= 0: that row is decoded greedily
 };
 
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
@@ -229,7 +230,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (c + i < c_end && vbase + i < p.V) {
-            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, nz[i]);
+            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? nz[i] : 0.f);
             if (y > bv) {
               bv = y;
               bi = vbase + i;
@@ -245,7 +246,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {
             const int i = g * 4 + wi;
-            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
+            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(w[wi]) : 0.f);
             if (c + i < c_end && vbase + i < p.V && y > bv) {
               bv = y;
               bi = vbase + i;
@@ -257,7 +258,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
         for (int i = 0; i < 32; ++i) {
           const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
           const uint4 q = noise_block(p.seed, s, e.b + p.b_offset, vg >> 2);
-          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
+          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)) : 0.f);
           if (c + i < c_end && vbase + i < p.V && y > bv) {
             bv = y;
             bi = vbase + i;
@@ -444,8 +445,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     const bool ret_logits = (p.flags & kFlagReturnLogits) != 0;
     const bool quad_aligned = (p.v_offset & 3) == 0;
     float invT = 1.0f;
-    if (row_ok && !greedy) invT = 1.0f / p.temperature[(size_t)b * p.temp_stride];
-    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT};
+    bool noisy = true;
+    if (row_ok && !greedy) {
+      const float temp = p.temperature[(size_t)b * p.temp_stride];
+      noisy = temp > 0.f;  // temperature <= 0 selects greedy decoding for this row
+      invT = noisy ? 1.0f / temp : 1.0f;
+    }
+    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy};
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * 2 + wg) * ((size_t)S * p.B);
 

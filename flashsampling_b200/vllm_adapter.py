@@ -1,0 +1,49 @@
+"""Sampler adapter in the shape an inference engine calls it (the caller side of the boundary).
+
+The reference is wired into its vLLM fork through a small class that receives the LM-head weight,
+the hidden states of the step and per-request sampling parameters and returns one token id per
+request (findings/vllm-integration.md:205-330, ``FMMSSampler.__call__``).  This mirrors that call
+without importing vLLM: per-request temperatures live in one device tensor, requests with
+temperature 0 are decoded greedily by the same kernel launch (their rows skip the noise), seeds
+advance per step, and nothing synchronises with the host.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .core import fused_mm_sample
+from .tp_info import TP1, TPInfo
+
+
+@dataclass
+class SamplingMetadata:
+    """The subset of an engine's per-step sampling state that this path consumes."""
+
+    temperature: torch.Tensor  # [num_requests] fp32 on the device; 0 = greedy for that request
+    all_greedy: bool = False  # every request greedy: skip temperature and noise altogether
+
+
+class FMMSSampler:
+    """``sampler(lm_head_weight, hidden_states, metadata) -> int32 [num_requests]`` token ids."""
+
+    def __init__(self, seed: int = 0, tp: TPInfo = TP1):
+        self.seed = int(seed)
+        self.step = 0
+        self.tp = tp
+
+    def __call__(self, lm_head_weight: torch.Tensor, hidden_states: torch.Tensor,
+                 sampling_metadata: SamplingMetadata) -> torch.Tensor:
+        self.step += 1
+        ids = fused_mm_sample(
+            weights=lm_head_weight,
+            hidden_states=hidden_states,
+            num_samples=1,
+            temperature=sampling_metadata.temperature,
+            seed=self.seed + self.step,  # draw s of a call uses stream seed + s: one fresh stream per step
+            greedy_sampling=sampling_metadata.all_greedy,
+            tp=self.tp,
+        )
+        return ids[:, 0].to(torch.int32)

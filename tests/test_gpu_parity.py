@@ -227,6 +227,45 @@ def test_two_stage_mode_gives_the_same_ids(fs):
     fs.check_status()
 
 
+@pytest.mark.parametrize("kernel,B", [("gemv", 4), ("mma", 48), ("mma", 200)])
+def test_rows_with_zero_temperature_are_greedy(fs, kernel, B):
+    """Per-row temperatures: rows with T = 0 take the argmax (an engine mixes greedy and sampled
+    requests in one batch); the other rows still follow their noise."""
+    V, D = 6000, 256
+    w, h = _head(V, D, B, w_std=0.08, seed=12)
+    temp = torch.full((B,), 0.8)
+    temp[::2] = 0.0
+    ids = fs.fused_mm_sample(w.to(_dev()), h.to(_dev()), 2, temp.to(_dev()), seed=9, kernel=kernel)
+    fs.check_status()
+    logits = O.logits_fp32(w, h)
+    noise = O.kernel_noise(9, 2, B, 0, V)
+    noise[:, ::2, :] = 0.0
+    t_eff = temp.clone()
+    t_eff[::2] = 1.0
+    _check_indices(ids, logits, t_eff, noise, f"mixed greedy {kernel}")
+    top2 = logits.topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 1e-3 * top2[:, 0].abs()
+    greedy_rows = torch.arange(B)[::2]
+    assert torch.equal(ids.cpu()[greedy_rows][clear[greedy_rows]][:, 0], logits.argmax(-1)[greedy_rows][clear[greedy_rows]])
+
+
+def test_engine_style_sampler_adapter(fs):
+    from flashsampling_b200.vllm_adapter import FMMSSampler, SamplingMetadata
+
+    V, D, B = 5000, 256, 6
+    w, h = _head(V, D, B, w_std=0.08, seed=2)
+    sampler = FMMSSampler(seed=100)
+    meta = SamplingMetadata(temperature=torch.tensor([0.0, 0.7, 1.0, 0.0, 1.3, 0.9], device=_dev()))
+    a = sampler(w.to(_dev()), h.to(_dev()), meta)
+    b = sampler(w.to(_dev()), h.to(_dev()), meta)
+    assert a.dtype == torch.int32 and a.shape == (B,)
+    ref = O.logits_fp32(w, h).argmax(-1)
+    assert int(a[0]) == int(ref[0]) and int(a[3]) == int(ref[3]) and int(b[0]) == int(ref[0])
+    greedy = sampler(w.to(_dev()), h.to(_dev()), SamplingMetadata(temperature=meta.temperature, all_greedy=True))
+    assert torch.equal(greedy.cpu().long(), ref)
+    fs.check_status()
+
+
 def test_argument_errors(fs):
     w = torch.zeros(64, 16, dtype=torch.bfloat16, device=_dev())
     h = torch.zeros(2, 24, dtype=torch.bfloat16, device=_dev())
