@@ -36,6 +36,8 @@ WORKLOADS = {
     "qwen": dict(V=151936, D=4096, w_std=0.02, temp=("scalar", 0.7), S=1, label="Qwen3-8B head"),
     "llama": dict(V=128256, D=8192, w_std=0.015, temp=("uniform", 0.5, 1.5), S=1, label="Llama-3-70B head"),
     "gemma": dict(V=262208, D=5376, w_std=0.02, temp=("scalar", 1.0), S=4, label="Gemma-3-27B head"),
+    "qwen_stress": dict(V=151936, D=4096, w_std=0.02, temp=("uniform", 0.3, 2.0), S=1,
+                        label="Qwen3-8B head, per-row temperatures"),
 }
 SWEEP_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 METRIC = "fused_sample_us_per_step"
