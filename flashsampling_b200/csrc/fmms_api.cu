@@ -590,6 +590,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   const size_t cap = workspace_item_capacity(workspace_bytes);
   p.ticket = reinterpret_cast<unsigned int*>(ws);
+  p.sched = p.ticket + 1;
   p.keys = reinterpret_cast<unsigned long long*>(ws + 256);
   p.cand_val = reinterpret_cast<float*>(ws + 256 + cap * 8);
   p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
@@ -640,7 +641,8 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
 
   if (flags & FMMS_FLAG_TWO_STAGE) {
     const int n = B * S;
-    reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.keys, B, S, v_global_offset, out_idx, out_val);
+    reduce_candidates_kernel<<<(n + 127) / 128, 128, 0, stream>>>(p.keys, p.sched, B, S, v_global_offset, out_idx,
+                                                                   out_val);
     return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
   }
   return FMMS_OK;

@@ -45,6 +45,7 @@ struct SampleParams {
   float* logits_out;         // [B, V]
   unsigned long long* keys;  // [S * B] packed winners, zero on entry and on exit (atomicMax target)
   unsigned int* ticket;      // CTAs-done counter, zero on entry and on exit
+  unsigned int* sched;       // dynamic work counter, zero on entry and on exit
   float* cand_val;           // [2 * gridDim.x, S * B] running per-CTA candidates (tensor-core path, S > 1)
   int* cand_idx;
   long long* out_idx;        // [B, S]
@@ -92,8 +93,11 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
       p.out_idx[(size_t)b * p.S + s] = p.v_offset + idx;
       if (p.out_val) p.out_val[(size_t)b * p.S + s] = v;
     }
-    if (tid == 0) *p.ticket = 0u;
-    if (tid == 0) stamp(p, 7);
+    if (tid == 0) {
+      *p.ticket = 0u;
+      *p.sched = 0u;
+      stamp(p, 7);
+    }
     return;
   }
   // Tensor parallel: this rank's winners go straight into every rank's exchange buffer (see
@@ -110,7 +114,10 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
     cand_key_decode(k, v, idx);
     tp_send(p.tp_peers, world, my_row + item, v, p.v_offset + idx, p.tp_epoch);
   }
-  if (tid == 0) *p.ticket = 0u;
+  if (tid == 0) {
+    *p.ticket = 0u;
+    *p.sched = 0u;
+  }
   for (int item = tid; item < n; item += nthreads) {
     float bv;
     long long bi;
@@ -132,7 +139,7 @@ __host__ __device__ inline int gemv_dpad(int D, int chunks) {
 
 __host__ __device__ inline size_t gemv_smem_bytes(int NB, int D, int stages, int chunks) {
   return (size_t)stages * chunks * gemv_stage_bytes(NB) + (size_t)NB * gemv_dpad(D, chunks) * 2 +
-         16 * (size_t)stages + kGemvConsumerWarps * 32 * 8 + 16;
+         16 * (size_t)stages + kGemvConsumerWarps * 32 * 8 + 16 + 4 * (size_t)stages;
 }
 
 __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t x) {
@@ -162,16 +169,20 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   float* red_val = reinterpret_cast<float*>(empty_bar + stages);
   int* red_idx = reinterpret_cast<int*>(red_val + kGemvConsumerWarps * 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(red_idx + kGemvConsumerWarps * 32);
+  volatile int* stage_group = abort_flag + 4;  // row group carried by each ring slot (-1: no more work)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
-  // contiguous range of row groups of this CTA
+  // Work split: every CTA first walks a contiguous range holding 7/8 of its even share of the
+  // 32(64)-row groups; the remaining groups form a pool that CTAs claim one at a time through an
+  // atomic counter, which evens out the differences in the bandwidth individual SMs get.
   const int groups_total = (p.V + kGemvRows - 1) / kGemvRows;
-  const int base = groups_total / (int)gridDim.x, rem = groups_total % (int)gridDim.x;
+  const int g_static = (int)(((long long)groups_total * 7 / 8) / (int)gridDim.x);
   const int cta = blockIdx.x;
-  const int g_begin = cta * base + min(cta, rem);
-  const int g_end = g_begin + base + (cta < rem ? 1 : 0);
+  const int g_begin = cta * g_static;
+  const int g_end = g_begin + g_static;
+  const int pool_begin = (int)gridDim.x * g_static;
 
   if (tid == 0) {
     for (int i = 0; i < stages; ++i) {
@@ -201,11 +212,27 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
       prefetch_tmap(&w_map);
       const uint64_t pol = policy_evict_first();
       int it = 0;
-      for (int g = g_begin; g < g_end; ++g) {
+      int g = g_begin < g_end ? g_begin : -1;
+      int claimed = -1;  // pool group claimed ahead of time (the atomic's latency hides behind a group)
+      bool from_pool = false;
+      if (g < 0) {
+        g = pool_begin + (int)atomicAdd(p.sched, 1u);
+        from_pool = true;
+      }
+      while (g < groups_total && !*abort_flag) {
+        // claim the next group before streaming this one
+        int g_next;
+        if (!from_pool && g + 1 < g_end) {
+          g_next = g + 1;
+        } else {
+          claimed = pool_begin + (int)atomicAdd(p.sched, 1u);
+          g_next = claimed;
+        }
         for (int kc = 0; kc < KC; ++kc, ++it) {
           const int st = it % stages;
           const uint32_t n = (uint32_t)(it / stages);
           if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) break;
+          stage_group[st] = g;
           mbar_arrive_expect_tx(&full_bar[st], kGemvStageBytes);
           if (CK == 1)
             tma_load_2d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, kc * kGemvCols, g * kGemvRows,
@@ -214,7 +241,17 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
             tma_load_3d_hint(w_tiles + (size_t)st * kGemvStageBytes, &w_map, 0, g * kGemvRows, kc * CK,
                              &full_bar[st], pol);
         }
-        if (*abort_flag) break;
+        if (g_next == claimed) from_pool = true;
+        g = g_next;
+      }
+      if (!*abort_flag) {
+        // end marker: one more ring slot, no data
+        const int st = it % stages;
+        const uint32_t n = (uint32_t)(it / stages);
+        if (mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) {
+          stage_group[st] = -1;
+          mbar_arrive(&full_bar[st]);
+        }
       }
       if (*abort_flag) {
         // A wait ran out somewhere: before the CTA may retire, give the copies that
@@ -246,7 +283,15 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   }
 
   int it = 0;
-  for (int g = g_begin; g < g_end; ++g) {
+  for (;;) {
+    // the first ring slot of a group tells which group it is
+    {
+      const int st = it % stages;
+      const uint32_t n = (uint32_t)(it / stages);
+      if (!mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev)) break;
+    }
+    const int g = stage_group[it % stages];
+    if (g < 0) break;
     float2 acc[kGemvRowsPerWarp][NB];
 #pragma unroll
     for (int r = 0; r < kGemvRowsPerWarp; ++r)
@@ -381,9 +426,11 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
 // Stand-alone second stage (FMMS_FLAG_TWO_STAGE): the sampling kernel only merges its
 // candidates into p.keys; this kernel decodes the winners and clears the keys.
 // ---------------------------------------------------------------------------------
-__global__ void reduce_candidates_kernel(unsigned long long* __restrict__ keys, int B, int S, long long v_offset,
-                                         long long* __restrict__ out_idx, float* __restrict__ out_val) {
+__global__ void reduce_candidates_kernel(unsigned long long* __restrict__ keys, unsigned int* __restrict__ sched,
+                                         int B, int S, long long v_offset, long long* __restrict__ out_idx,
+                                         float* __restrict__ out_val) {
   const int item = blockIdx.x * blockDim.x + threadIdx.x;  // s * B + b
+  if (item == 0) *sched = 0u;  // the sampling kernel's dynamic work counter
   if (item >= B * S) return;
   const unsigned long long k = keys[item];
   keys[item] = 0ull;
