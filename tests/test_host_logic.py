@@ -107,3 +107,23 @@ def test_tp_buffer_size(lib):
     assert lib.fmms_tp_buffer_bytes(8, 1024, ctypes.byref(n)) == 0
     assert n.value == 2 * 8 * 1024 * 16 + 8 * 128
     assert lib.fmms_tp_buffer_bytes(9, 1024, ctypes.byref(n)) != 0
+
+
+def test_reference_import_names_resolve_through_the_shim():
+    import sys
+
+    sys.path.insert(0, str(ROOT / "flashsampling_b200" / "compat"))
+    try:
+        from fused_mm_sampling.core import fused_mm_sample_triton, get_sampler  # noqa: F401
+        from fused_mm_sampling.testing import make_synthetic_inputs
+        from fused_mm_sampling.tp_info import TP1, TPInfo
+
+        import flashsampling_b200 as fs
+
+        assert fused_mm_sample_triton is fs.fused_mm_sample and TP1 == TPInfo(0, 1)
+        inp = make_synthetic_inputs(vocab_size=100, n_hidden_states=1, device="cpu")
+        assert inp.weights.shape == (100, 16)
+    finally:
+        sys.path.pop(0)
+        for m in [k for k in sys.modules if k.startswith("fused_mm_sampling")]:
+            del sys.modules[m]
