@@ -8,12 +8,12 @@ A step is one sampling call over one batch of hidden states: W[V, d] bf16 is
 streamed once, B rows get one token id each.  Default workload: the Qwen3-8B
 head (V=151936, d=4096, T=0.7, 1 draw per row) at B=64 on one GPU; N > 1 shards
 the vocabulary contiguously over N GPUs (tensor parallel, strong scaling).
-The metric is microseconds per step with cold weight reads (the weight is far
-larger than L2 and every step streams a different copy of it): exactly K
-back-to-back steps between one pair of CUDA events on the launching stream,
-barrier + synchronize on both sides, maximum over ranks, divided by K.  Per-call
-event times (L2 swept before each call) and the reference's own protocol (a
-256 MB buffer zeroed before each call) are reported beside it.  One JSON line is
+The metric is microseconds per step with cold weight reads: K steps bracketed by
+barrier + synchronize, one pair of CUDA events per step on the launching stream
+(a read-only sweep evicts L2 before each step and the weight copy is rotated),
+maximum over ranks per step, median over the K steps.  The same K steps run
+back to back between one event pair, and the reference's own protocol (a 256 MB
+buffer zeroed before each call), are reported beside it.  One JSON line is
 printed by rank 0.
 """
 
@@ -306,12 +306,12 @@ def run_b200(args):
     if args.sweep and world == 1:
         for b in SWEEP_BATCHES:
             r = measure(b, max(10, args.steps // 4), max(3, args.warmup // 4), with_e2e=False) if b != B else main
-            us = r["region_ms"] * 1e3
+            us = statistics.median(r["times_ms"]) * 1e3
             gbs = algorithmic_bytes(V, D, b, S) / (us * 1e-6) / 1e9
             sweep.append(dict(B=b, us=round(us, 2), path=r["path"], algo_gbs=round(gbs, 1),
                               frac_of_8tbs=round(gbs / 8000, 4), x_weight_read_at_8tbs=round(us / (2 * V * D / 8e12 * 1e6), 4),
                               tflops=round(2.0 * V * D * b / (us * 1e-6) / 1e12, 1),
-                              per_call_event_us=round(statistics.median(r["times_ms"]) * 1e3, 2),
+                              back_to_back_us=round(r["region_ms"] * 1e3, 2),
                               write_flush_us=round(statistics.median(r["ref_times_ms"]) * 1e3, 2)))
 
     if rank != 0:
@@ -319,9 +319,9 @@ def run_b200(args):
             dist.destroy_process_group()
         return
     v_local = V // world
-    med_us = main["region_ms"] * 1e3
-    mean_ms = main["region_ms"]
     per_call = sorted(main["times_ms"])
+    med_us = statistics.median(per_call) * 1e3
+    mean_ms = statistics.fmean(per_call)
     peak, peak_kind = measured_peaks()
     ach = algorithmic_bytes(v_local, D, B, S) / (mean_ms * 1e-3) / 1e9
     flops = 2.0 * v_local * D * B
@@ -349,18 +349,21 @@ def run_b200(args):
                         f"vocabulary sharded over {world} GPU(s)",
             "batch": B, "vocab": V, "hidden": D, "num_samples": S, "tensor_parallel": world,
             "kernel": main["path"],
-            "l2": f"inputs larger than L2: every step streams a different copy of the {v_local * D * 2 / 1e6:.0f} MB weight "
-                  f"(shard), {main['n_copies']} copies in rotation ({main['n_copies'] * v_local * D * 2 / 1e9:.2f} GB between reuses)",
+            "l2": f"cold: a read-only sweep of a 256 MB buffer evicts L2 before every timed call (no dirty lines), and every "
+                  f"step streams a different copy of the {v_local * D * 2 / 1e6:.0f} MB weight (shard), {main['n_copies']} "
+                  f"copies in rotation",
             "timing": "CUDA events per call on the launch stream, max over ranks, median over steps",
         },
-        "per_call_event_us": {"median": round(statistics.median(per_call) * 1e3, 3),
-                              "p10": round(per_call[len(per_call) // 10] * 1e3, 3),
-                              "p90": round(per_call[(len(per_call) * 9) // 10] * 1e3, 3),
-                              "note": "one event pair per call, read-only 256 MB L2 sweep before each call"},
+        "p10_us": round(per_call[len(per_call) // 10] * 1e3, 3),
+        "p90_us": round(per_call[(len(per_call) * 9) // 10] * 1e3, 3),
+        "back_to_back_us": round(main["region_ms"] * 1e3, 3),
+        "back_to_back_note": "the same K steps enqueued back to back between ONE event pair (no sweep, cold reads by weight "
+                             "rotation), max over ranks / K; with several ranks this figure follows the slowest Python "
+                             "launch loop, not the GPUs",
         "write_flush_protocol_us": round(statistics.median(main["ref_times_ms"]) * 1e3, 3),
         "write_flush_protocol_note": "the reference's protocol: a 256 MB buffer is zeroed before each timed call; its "
                                      "dirty lines are written back during the timed kernel",
-        "clocks": main["clocks_region"] if main["clocks_region"]["samples"] else main["clocks"],
+        "clocks": main["clocks"] if main["clocks"]["samples"] else main["clocks_region"],
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
