@@ -104,7 +104,13 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   // fmms_tp.cuh for the protocol), then the same threads wait for the peers' records and keep
   // the maximum.  Items are processed in rounds of `nthreads`: send a round, then receive it.
   const int world = p.tp_world, rank = p.tp_rank;
-  const int parity = (int)(p.tp_epoch & 1u);
+  unsigned int epoch = p.tp_epoch;
+  unsigned int* counter = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(p.tp_peers.slots[rank]) +
+                                                          tp_counter_offset(world, p.tp_max_items));
+  if (epoch == 0u) epoch = tp_load_counter(counter) + 1u;  // step counter kept on the device (replayable)
+  sync();
+  if (tid == 0) *counter = epoch;
+  const int parity = (int)(epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * p.tp_max_items;
   const TpRecord* mine = p.tp_peers.slots[rank] + (size_t)parity * world * p.tp_max_items;
   for (int item = tid; item < n; item += nthreads) {
@@ -112,7 +118,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
     float v;
     int idx;
     cand_key_decode(k, v, idx);
-    tp_send(p.tp_peers, world, my_row + item, v, p.v_offset + idx, p.tp_epoch);
+    tp_send(p.tp_peers, world, my_row + item, v, p.v_offset + idx, epoch);
   }
   if (tid == 0) {
     *p.ticket = 0u;
@@ -121,7 +127,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   for (int item = tid; item < n; item += nthreads) {
     float bv;
     long long bi;
-    if (!tp_recv_max(mine, world, p.tp_max_items, item, p.tp_epoch, p.tp_wait_ns, bv, bi)) {
+    if (!tp_recv_max(mine, world, p.tp_max_items, item, epoch, p.tp_wait_ns, bv, bi)) {
       if (p.status_dev) atomicExch(p.status_dev, kErrTimeout);
       bi = -1;
     }

@@ -17,7 +17,8 @@
 namespace fmms {
 
 constexpr int kTpMaxWorld = 8;
-constexpr int kTpFlagStride = 32;  // reserved tail of the buffer (kept for layout compatibility)
+constexpr int kTpFlagStride = 32;  // the buffer ends with world * 128 reserved bytes; the first word is the
+                                   // rank's own step counter (used when the caller passes epoch 0)
 
 struct TpRecord {
   unsigned int val_bits, epoch0, idx, epoch1;
@@ -30,6 +31,18 @@ struct TpPeers {
 
 __host__ __device__ inline size_t tp_buffer_bytes(int world, int max_items) {
   return (size_t)2 * world * max_items * sizeof(TpRecord) + (size_t)world * kTpFlagStride * 4;
+}
+
+__host__ __device__ inline size_t tp_counter_offset(int world, int max_items) {
+  return (size_t)2 * world * max_items * sizeof(TpRecord);
+}
+
+// Epoch of this step: the caller's, or (caller passed 0) one more than the count kept in the
+// rank's own buffer, which makes a captured launch replayable: every replay advances by itself.
+__device__ __forceinline__ unsigned int tp_load_counter(const unsigned int* counter) {
+  unsigned int v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void st_record(TpRecord* p, float v, unsigned int idx, unsigned int epoch) {
@@ -88,6 +101,11 @@ __global__ void tp_exchange_kernel(const long long* __restrict__ local_idx, cons
                                    unsigned int epoch, unsigned long long wait_limit_ns,
                                    long long* __restrict__ out_idx, float* __restrict__ out_val, int* status_dev) {
   const int tid = threadIdx.x;
+  unsigned int* counter = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(peers.slots[rank]) +
+                                                          tp_counter_offset(world, max_items));
+  if (epoch == 0u) epoch = tp_load_counter(counter) + 1u;
+  __syncthreads();  // every thread has read the counter before thread 0 advances it
+  if (tid == 0) *counter = epoch;
   const int parity = (int)(epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * max_items;
   const TpRecord* mine = peers.slots[rank] + (size_t)parity * world * max_items;

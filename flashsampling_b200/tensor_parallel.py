@@ -114,8 +114,9 @@ class PeerExchange:
         return self.tp.rank * v_local
 
     def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
+        """0 = the step number lives in the exchange buffer and the kernels advance it themselves,
+        so a captured step can be replayed (CUDA graphs) and host and device never disagree."""
+        return 0
 
     def reduce(self, ids: torch.Tensor, vals: torch.Tensor):
         flat_ids, flat_vals = ids.reshape(-1), vals.reshape(-1)
@@ -125,10 +126,9 @@ class PeerExchange:
         with torch.cuda.device(self.device):
             for lo in range(0, n, self.max_items):
                 cnt = min(self.max_items, n - lo)
-                self.epoch += 1
                 rc = self.lib.fmms_tp_exchange(
                     flat_ids[lo:].data_ptr(), flat_vals[lo:].data_ptr(), cnt, self.max_items, self.tp.rank,
-                    self.tp.size, self.ptrs, self.epoch, 0, out_ids[lo:].data_ptr(), out_vals[lo:].data_ptr(),
+                    self.tp.size, self.ptrs, self.next_epoch(), 0, out_ids[lo:].data_ptr(), out_vals[lo:].data_ptr(),
                     self.status.data_ptr(), stream,
                 )
                 _lib.check(rc, "fmms_tp_exchange")

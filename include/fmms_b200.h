@@ -167,8 +167,10 @@ int fmms_tp_close(void* peer_ptr);
 int fmms_tp_free(void* dev_ptr);
 
 /* The exchange step (one small kernel).  `peer_buffers[world]` are the device pointers of
- * every rank's buffer as seen from this process (own buffer at index `rank`); `epoch` must
- * be the same on all ranks and grow by one per step, starting at 1; `wait_limit_ns` bounds
+ * every rank's buffer as seen from this process (own buffer at index `rank`); `epoch` is
+ * either 0 - the step number is then kept in the rank's own buffer and advanced by the kernel,
+ * so a launch captured in a CUDA graph can be replayed - or the caller's own counter, the
+ * same on all ranks and growing by one per step from 1 (do not mix the two on one buffer); `wait_limit_ns` bounds
  * the wait for the peers' records (0 = 2 s), after which FMMS_ERR_TIMEOUT is written to `status_dev` and the
  * ids are set to -1.  Replaces symm_mem_hdl.barrier() + _local_reduce over world * tiles
  * (tensor_parallel_reduce.py:77-84). */

@@ -266,6 +266,31 @@ def test_engine_style_sampler_adapter(fs):
     fs.check_status()
 
 
+@pytest.mark.parametrize("kernel,B", [("gemv", 2), ("mma", 40), ("mma", 160)])
+def test_step_replays_inside_a_cuda_graph(fs, kernel, B):
+    """Engines replay decode steps as CUDA graphs: a captured sampling call must give the eager ids
+    on every replay (the kernels leave their workspace ready for the next launch by themselves)."""
+    V, D, S = 40000, 256, 2
+    w, h = _head(V, D, B, w_std=0.08, seed=6)
+    w, h = w.to(_dev()), h.to(_dev())
+    t = torch.tensor(0.8, device=_dev())
+    eager = fs.fused_mm_sample(w, h, S, t, seed=21, kernel=kernel)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fs.fused_mm_sample(w, h, S, t, seed=21, kernel=kernel)  # warm-up on the capture stream
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        captured = fs.fused_mm_sample(w, h, S, t, seed=21, kernel=kernel)
+    for _ in range(3):
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, eager)
+    fs.check_status()
+
+
 def test_argument_errors(fs):
     w = torch.zeros(64, 16, dtype=torch.bfloat16, device=_dev())
     h = torch.zeros(2, 24, dtype=torch.bfloat16, device=_dev())

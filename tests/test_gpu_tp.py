@@ -35,6 +35,29 @@ def _tp_worker(world):
                 assert torch.equal(got, full), (mode, rep, tp.rank, (got != full).sum().item())
         fs.check_status()
     os.environ["FMMS_TP_EXCHANGE"] = "p2p"
+    # a captured tensor-parallel step replays: the exchange keeps its step counter on the device
+    V, D, B, S = 16384 - 16384 % world, 256, 32, 1
+    w, h = gaussian_head(V, D, B, 0.08, seed=3)
+    t = torch.tensor(0.9, device=dev)
+    full = fs.fused_mm_sample(w.to(dev), h.to(dev), S, t, seed=5, kernel="mma")
+    w_local = shard_weights(w, tp).contiguous().to(dev)
+    hd = h.to(dev)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fs.fused_mm_sample(w_local, hd, S, t, seed=5, tp=tp, kernel="mma")
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        captured = fs.fused_mm_sample(w_local, hd, S, t, seed=5, tp=tp, kernel="mma")
+    for _ in range(4):
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, full), (tp.rank, (captured != full).sum().item())
+    got = fs.fused_mm_sample(w_local, hd, S, t, seed=5, tp=tp, kernel="mma")  # eager again, same counter
+    assert torch.equal(got, full)
+    fs.check_status()
     # the reference's distributed protocol: chi-square per rank on sharded ramps (testing.py:264-275)
     for V, nh in ((256, 2), (512, 1)):
         assert_sampling_distribution("fused-triton", V, nh, tp=tp)
