@@ -1,14 +1,17 @@
-// Small-batch weight-streaming kernel (batch rows <= 8).
+// Small-batch weight-streaming kernel (batch rows <= 8) and the pieces every sampling kernel
+// shares: the parameter block and the tail that decodes the winners (and, with tensor
+// parallelism, exchanges them over NVLink).
 //
-// A persistent grid of one CTA per SM walks contiguous ranges of 32-row groups of
-// W[V, D].  A producer warp streams 32 x 256 bf16 boxes (16 KiB) of W through a
-// shared-memory ring with TMA (cp.async.bulk.tensor) and mbarriers; eight consumer
-// warps each own four rows of the group and accumulate fp32 dot products against
-// the hidden states, which sit in shared memory for the whole kernel.  When a group
-// is complete the sums are reduced across the warp, scaled by 1/T, perturbed with
-// Gumbel noise and folded into a running (max, index) per (row b, draw s) that
-// lives in registers for the whole CTA; one candidate per (b, s) per CTA reaches
-// global memory.
+// A persistent grid of one CTA per SM.  A producer warp streams row groups of W[V, D] - 32 rows
+// (64 for two to four batch rows) by one or two 256-column chunks per TMA operation
+// (cp.async.bulk.tensor, 16 to 64 KiB) - through a shared-memory ring with mbarriers; eight
+// consumer warps each own four (eight) rows of the group and accumulate fp32 dot products
+// (packed fma.rn.f32x2) against the hidden states, which sit in shared memory for the whole
+// kernel.  When a group is complete the sums are reduced across the warp, scaled by 1/T,
+// perturbed with Gumbel noise and folded into a running (max, index) per (row b, draw s) that
+// lives in registers for the whole CTA.  Groups are dealt out 7/8 statically (contiguous ranges)
+// and 1/8 through an atomic counter, because SMs do not all get the same share of the HBM
+// bandwidth.  One packed candidate per (b, s) per CTA reaches global memory (atomicMax).
 #pragma once
 
 #include <cuda.h>
@@ -28,7 +31,7 @@ __host__ __device__ constexpr int gemv_rows(int NB) { return kGemvConsumerWarps 
 __host__ __device__ constexpr int gemv_stage_bytes(int NB) { return gemv_rows(NB) * kGemvCols * 2; }
 constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer warp
 constexpr int kGemvMaxBatch = 8;
-constexpr int kGemvMaxStages = 6;  // ~96 KiB in flight per SM: deeper rings measured slower
+constexpr int kGemvMaxStages = 6;  // ring depth cap: ~96-128 KiB in flight per SM, deeper rings measured slower
 
 struct SampleParams {
   const __nv_bfloat16* H;    // [B, D]
