@@ -19,7 +19,7 @@
 namespace fmms {
 
 constexpr int kVersion = 1000;
-constexpr int kMaxParts = 320;      // upper bound on candidate rows in the workspace (2 per persistent CTA)
+constexpr int kMaxParts = 640;      // upper bound on candidate rows in the workspace (4 per persistent CTA)
 constexpr int kMaxDevices = 16;
 constexpr int kGemvAutoMaxBatch = 2;  // auto-dispatch: batches up to this use the weight-streaming kernel (measured crossover)
 
@@ -311,7 +311,7 @@ static int build_umma_maps(const void* W, const void* H, const SampleParams& p, 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
   UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
                           umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force());
-  if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
+  if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
   CUtensorMap wq, wq1, hm;
   int rc = build_umma_maps(W, H, p, pl, &wq, &wq1, &hm);
   if (rc != kOk && pl.slabs > 1) {
@@ -326,7 +326,7 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   p.tiles_per_cta = pl.tiles_per_cta;
   rc = pl.mt == 1 ? launch_umma_mt<1>(d, wq, wq1, hm, p, pl, stream) : launch_umma_mt<2>(d, wq, wq1, hm, p, pl, stream);
   if (rc != kOk) return -rc;
-  return pl.grid * 2;
+  return pl.grid * kUmmaEpiGroups;
 }
 
 // ---- CTA-pair tensor-core launch (129..256 batch rows) -----------------------------------
@@ -345,7 +345,7 @@ static bool use_pair_kernel(int V, int D, int B, int num_sms) {
 
 static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
   const PairPlan pl = pair_plan(p.V, p.D, d.num_sms, d.max_smem_optin, umma_slabs_force());
-  if (pl.grid * 2 > kMaxParts) return -kErrUnsupported;
+  if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
   CUtensorMap wq, wq1, hm;
   int rc = get_tensor_map_slabs(W, p.V, p.D, pl.q_units * 16, pl.slabs, &wq);
   if (rc != kOk) return -rc;
@@ -368,7 +368,7 @@ static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleP
   umma_pair_sample_kernel<<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total, pl.q_units,
                                                                       pl.slabs);
   if (cudaGetLastError() != cudaSuccess) return -kErrCuda;
-  return pl.grid * 2;
+  return pl.grid * kUmmaEpiGroups;
 }
 
 // ---- measurement helper: evict L2 with a read-only sweep (leaves no dirty lines behind) ----
@@ -485,7 +485,7 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
       plan[4] = pp.stages;
       plan[5] = 2;
       plan[6] = (int)pp.smem;
-      plan[7] = pp.grid * 2;
+      plan[7] = pp.grid * kUmmaEpiGroups;
       return FMMS_OK;
     }
     const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0);
@@ -496,7 +496,7 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
     plan[4] = pl.stages;
     plan[5] = pl.mt;
     plan[6] = (int)pl.smem;
-    plan[7] = pl.grid * 2;
+    plan[7] = pl.grid * kUmmaEpiGroups;
   }
   return FMMS_OK;
 }

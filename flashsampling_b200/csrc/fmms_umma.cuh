@@ -25,9 +25,11 @@
 
 namespace fmms {
 
-constexpr int kUmmaThreads = 384;
+constexpr int kUmmaThreads = 640;
 constexpr int kUmmaEpiWarp0 = 4;       // first epilogue warp
-constexpr int kUmmaEpiWarps = 8;       // two warpgroups
+constexpr int kUmmaEpiWarps = 16;      // four warpgroups: four warps per scheduler keep the epilogue's
+                                       // long dependency chains (Philox, logarithms) overlapped
+constexpr int kUmmaEpiGroups = kUmmaEpiWarps / 4;
 constexpr int kUmmaBK = 64;            // hidden-dimension slice per stage (128 B of bf16)
 constexpr int kUmmaHTileMax = 128 * 128;  // the MMA always reads 128 hidden-state rows (16 KiB)
 constexpr int kUmmaMaxStages = 12;
@@ -314,10 +316,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  // S > 1 keeps the running candidates of each (row, draw) in global memory: two rows per CTA
-  // (one per epilogue warpgroup), which start as "none"
+  // S > 1 keeps the running candidates of each (row, draw) in global memory: one row per CTA and
+  // epilogue warpgroup, which start as "none"
   if (p.S > 1) {
-    const int n = 2 * p.S * p.B;
+    const int n = kUmmaEpiGroups * p.S * p.B;
     float* cv = p.cand_val + (size_t)cta * n;
     int* ci = p.cand_idx + (size_t)cta * n;
     for (int i = tid; i < n; i += kUmmaThreads) {
@@ -432,10 +434,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
   } else if (warp >= kUmmaEpiWarp0) {
     // -------------------------------- epilogue --------------------------------
-    const int ew = warp - kUmmaEpiWarp0;  // 0..7
-    const int wg = ew >> 2;               // epilogue warpgroup
+    const int ew = warp - kUmmaEpiWarp0;  // 0..15
+    const int wg = ew >> 2;               // epilogue warpgroup 0..3
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-    const int m_tile = (MT == 2) ? wg : 0;
+    // MT = 1: the four warpgroups split a tile's columns four ways; MT = 2: two per M tile
+    const int m_tile = (MT == 2) ? (wg & 1) : 0;
+    const int col_group = (MT == 2) ? (wg >> 1) : wg;
+    constexpr int kColGroups = (MT == 2) ? kUmmaEpiGroups / 2 : kUmmaEpiGroups;
     const int b = m_tile * 128 + quad * 32 + lane;
     const bool row_ok = b < p.B;
     const bool warp_ok = (m_tile * 128 + quad * 32) < p.B;
@@ -453,7 +458,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy};
     const int S = p.S;
-    const size_t slot_row = ((size_t)cta * 2 + wg) * ((size_t)S * p.B);
+    const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
 
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
@@ -463,10 +468,11 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       int v0, NT;
       walk.next(v0, NT);
       if (NT == 0) continue;
-      // column range of this warp inside the tile: MT = 1 splits the tile between the warpgroups
-      const int half = ((NT / 2) + 31) / 32 * 32;
-      const int c_begin = (MT == 2) ? 0 : (wg == 0 ? 0 : min(half, NT));
-      const int c_end = (MT == 2) ? NT : (wg == 0 ? min(half, NT) : NT);
+      // column range of this warp inside the tile: whole 32-column chunks, dealt out evenly
+      const int chunks = (NT + 31) / 32;
+      const int per_group = (chunks + kColGroups - 1) / kColGroups;
+      const int c_begin = min(col_group * per_group * 32, NT);
+      const int c_end = min(c_begin + per_group * 32, NT);
       const int j = ta % acc_stages;
       const uint32_t un = (uint32_t)(ta / acc_stages);
       ++ta;

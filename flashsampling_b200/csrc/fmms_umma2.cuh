@@ -186,7 +186,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     tmem_relinquish_pair();
   }
   if (p.S > 1) {
-    const int n = 2 * p.S * p.B;
+    const int n = kUmmaEpiGroups * p.S * p.B;
     float* cv = p.cand_val + (size_t)cta * n;
     int* ci = p.cand_idx + (size_t)cta * n;
     for (int i = tid; i < n; i += kUmmaThreads) {
@@ -304,7 +304,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     const EpiRow row{b, row_ok, greedy, (p.flags & kFlagExtNoise) != 0, (p.flags & kFlagReturnLogits) != 0,
                      (p.v_offset & 3) == 0, invT, noisy};
     const int S = p.S;
-    const size_t slot_row = ((size_t)cta * 2 + wg) * ((size_t)S * p.B);
+    const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
     float best_val = -INFINITY;
     int best_idx = kIdxNone;
 
@@ -313,9 +313,10 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
       int v0, NT;
       walk.next(v0, NT);
       if (NT == 0) continue;
-      const int half = ((NT / 2) + 31) / 32 * 32;
-      const int c_begin = wg == 0 ? 0 : min(half, NT);
-      const int c_end = wg == 0 ? min(half, NT) : NT;
+      const int chunks = (NT + 31) / 32;
+      const int per_group = (chunks + kUmmaEpiGroups - 1) / kUmmaEpiGroups;
+      const int c_begin = min(wg * per_group * 32, NT);
+      const int c_end = min(c_begin + per_group * 32, NT);
       const int j = ta % acc_stages;
       const uint32_t un = (uint32_t)(ta / acc_stages);
       ++ta;
