@@ -266,17 +266,22 @@ static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream
 }
 
 // ---- tensor-core launch -----------------------------------------------------------
+struct UmmaMaps {
+  CUtensorMap wq, wq1, hm, wt1, wt2, hmt;
+};
+
 template <int MT>
-static int launch_umma_mt(DeviceInfo& d, const CUtensorMap& wq, const CUtensorMap& wq1, const CUtensorMap& hm,
-                          SampleParams& p, const UmmaPlan& pl, cudaStream_t stream) {
+static int launch_umma_mt(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
+                          cudaStream_t stream) {
   if (!d.umma_attr[MT]) {
     if (cudaFuncSetAttribute(umma_sample_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              d.max_smem_optin) != cudaSuccess)
       return kErrCuda;
     d.umma_attr[MT] = true;
   }
-  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.nt_cap, pl.units_total,
-                                                                     pl.q_units, pl.h_rows, pl.slabs);
+  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
+      mp.wq, mp.wq1, mp.hm, mp.wt1, mp.wt2, mp.hmt, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs,
+      pl.tail1_units, pl.tail2_units, pl.tail_slabs);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
@@ -285,46 +290,64 @@ static int umma_slabs_force() {
   return v;
 }
 
-static int build_umma_maps(const void* W, const void* H, const SampleParams& p, const UmmaPlan& pl,
-                           CUtensorMap* wq, CUtensorMap* wq1, CUtensorMap* hm) {
+static int umma_tails() {
+  static const int v = env_int("FMMS_UMMA_TAILS");  // 0 (default): off; 1: 64- and 32-row closing tiles; 2: 64-row only
+  return v;
+}
+
+static int build_umma_maps(const void* W, const void* H, const SampleParams& p, const UmmaPlan& pl, UmmaMaps* mp) {
   int rc;
-  if (pl.slabs > 1) {
-    rc = get_tensor_map_slabs(W, p.V, p.D, pl.q_units * 16, pl.slabs, wq);
+  if (pl.slabs > 1 || pl.tail1_units) {
+    rc = get_tensor_map_slabs(W, p.V, p.D, pl.q_units * 16, pl.slabs, &mp->wq);
     if (rc != kOk) return rc;
-    *wq1 = *wq;
+    mp->wq1 = mp->wq;
     if (pl.q_units > 1) {
-      rc = get_tensor_map_slabs(W, p.V, p.D, (pl.q_units - 1) * 16, pl.slabs, wq1);
+      rc = get_tensor_map_slabs(W, p.V, p.D, (pl.q_units - 1) * 16, pl.slabs, &mp->wq1);
       if (rc != kOk) return rc;
     }
-    return get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.slabs, hm);
-  }
-  rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, wq);
-  if (rc != kOk) return rc;
-  *wq1 = *wq;  // a CTA only uses the lower box when some tile is one unit shorter
-  if (pl.q_units > 1) {
-    rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, wq1);
+    rc = get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.slabs, &mp->hm);
+    if (rc != kOk) return rc;
+  } else {
+    rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->wq);
+    if (rc != kOk) return rc;
+    mp->wq1 = mp->wq;  // a CTA only uses the lower box when some tile is one unit shorter
+    if (pl.q_units > 1) {
+      rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->wq1);
+      if (rc != kOk) return rc;
+    }
+    rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->hm);
     if (rc != kOk) return rc;
   }
-  return get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, hm);
+  mp->wt1 = mp->wt2 = mp->wq;
+  mp->hmt = mp->hm;
+  if (pl.tail1_units) {
+    rc = get_tensor_map_slabs(W, p.V, p.D, pl.tail1_units * 16, pl.tail_slabs, &mp->wt1);
+    if (rc != kOk) return rc;
+    rc = get_tensor_map_slabs(W, p.V, p.D, pl.tail2_units * 16, pl.tail_slabs, &mp->wt2);
+    if (rc != kOk) return rc;
+    rc = get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.tail_slabs, &mp->hmt);
+    if (rc != kOk) return rc;
+  }
+  return kOk;
 }
 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
   UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
-                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force());
+                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), umma_tails());
   if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
-  CUtensorMap wq, wq1, hm;
-  int rc = build_umma_maps(W, H, p, pl, &wq, &wq1, &hm);
-  if (rc != kOk && pl.slabs > 1) {
-    // the driver refused the 3-D view: fall back to one slab per operation
+  UmmaMaps mp;
+  int rc = build_umma_maps(W, H, p, pl, &mp);
+  if (rc != kOk && (pl.slabs > 1 || pl.tail1_units)) {
+    // the driver refused the 3-D view: fall back to one slab per operation, no closing tiles
     pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(),
-                   umma_min_tiles(), 0, 0);
-    rc = build_umma_maps(W, H, p, pl, &wq, &wq1, &hm);
+                   umma_min_tiles(), 0, 0, 0);
+    rc = build_umma_maps(W, H, p, pl, &mp);
   }
   if (rc != kOk) return -rc;
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * 16;
   p.tiles_per_cta = pl.tiles_per_cta;
-  rc = pl.mt == 1 ? launch_umma_mt<1>(d, wq, wq1, hm, p, pl, stream) : launch_umma_mt<2>(d, wq, wq1, hm, p, pl, stream);
+  rc = pl.mt == 1 ? launch_umma_mt<1>(d, mp, p, pl, stream) : launch_umma_mt<2>(d, mp, p, pl, stream);
   if (rc != kOk) return -rc;
   return pl.grid * kUmmaEpiGroups;
 }
@@ -488,11 +511,11 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
       plan[7] = pp.grid * kUmmaEpiGroups;
       return FMMS_OK;
     }
-    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0);
+    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0, umma_tails());
     plan[0] = FMMS_PATH_MMA;
     plan[1] = pl.grid;
     plan[2] = pl.q_units * 16;
-    plan[3] = pl.tiles_per_cta;
+    plan[3] = pl.tiles_per_cta + (pl.tail1_units ? 1 : 0) + (pl.tail2_units ? 1 : 0);
     plan[4] = pl.stages;
     plan[5] = pl.mt;
     plan[6] = (int)pl.smem;

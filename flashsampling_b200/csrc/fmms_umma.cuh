@@ -45,8 +45,12 @@ struct UmmaPlan {
   int h_rows;         // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
   int mt;             // M tiles (1 or 2)
   int slabs;          // 64-column K slabs per pipeline stage (one TMA operation fetches them all)
+  int tail1_units, tail2_units;  // two short closing tiles per CTA (0 = none), see umma_plan
+  int tail_slabs;     // K slabs per stage for the closing tiles
   size_t smem;
 };
+
+constexpr int kTail1Units = 4, kTail2Units = 2;  // closing tiles of 64 and 32 rows
 
 // Shared memory: [barriers 1 KiB][stages x (W tile: tallest tile x 128 B | MT hidden-state tiles:
 // h_rows x 128 B)][16 KiB slack].  With fewer than 128 hidden-state rows the MMA's 128-row A
@@ -55,13 +59,20 @@ struct UmmaPlan {
 __host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows, int slabs) {
   return (size_t)slabs * ((size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128);
 }
+// with closing tiles: the stage must also hold tail_slabs x (64 rows of W + the hidden-state slab)
+__host__ __device__ inline size_t umma_stage_bytes_tail(int mt, int q_units, int h_rows, int slabs, int tail_slabs) {
+  const size_t big = umma_stage_bytes(mt, q_units, h_rows, slabs);
+  const size_t tail = (size_t)tail_slabs * ((size_t)kTail1Units * 16 * 128 + (size_t)mt * h_rows * 128);
+  return big > tail ? big : tail;
+}
 
 // Work split.  The vocabulary is dealt out in units of 16 rows: CTA c gets a contiguous range
 // of U_c = units_total / grid (+1 for the first units_total % grid CTAs) units and cuts it into
 // T near-equal tiles, so no CTA walks more than 16 rows beyond the average.  All tiles of all
 // CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
-                                   int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1, int D = 0, int slabs_force = 0) {
+                                   int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1, int D = 0, int slabs_force = 0,
+                                   int tails = 0) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
@@ -70,8 +81,31 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.nt_cap = pl.mt == 1 ? 256 : mt2_nt_cap;
   pl.units_total = (V + 15) / 16;
   pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
-  const int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
+  int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
+  pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
+  // Closing tiles (off by default).  The epilogue of a tile (Philox + two logarithms per element,
+  // all rows of a TMEM lane quadrant on ONE scheduler) takes ~10 us for 208 columns and only the
+  // last one is exposed.  Ending every CTA's range with a 64-row (and a 32-row) tile shortens the
+  // exposed epilogue to ~4 us, but measured slower overall (Qwen head, B = 64: 213-220 us against
+  // 201 us): the short tiles' mainloops run well below the streaming rate and the previous big
+  // tile's epilogue still has to finish first.
+  pl.tail1_units = pl.tail2_units = 0;
+  pl.tail_slabs = 1;
+  if (tails && pl.mt == 1 && D > 0 && D % 64 == 0 && pl.h_rows <= 64 && u_max >= 24 && nt_target == 0 &&
+      min_tiles <= 1) {
+    pl.tail1_units = kTail1Units;
+    pl.tail2_units = tails == 1 ? kTail2Units : 0;  // tails == 2: one closing tile only
+    pl.tail_slabs = D / 64 < 4 ? D / 64 : 4;
+    u_max -= pl.tail1_units + pl.tail2_units;  // what remains for the big tiles
+  }
   int cap_units = pl.nt_cap / 16;
+  if (pl.mt == 1 && pl.h_rows <= 64 && D > 0 && D % 64 == 0) {
+    // keep tiles low enough for two K slabs per stage and three stages (the 52 KiB operations
+    // are worth more than the last 48 rows of tile height)
+    const long long per_stage = ((long long)max_smem - (1024 + 1024 + kUmmaHTileMax)) / 3;
+    const int fit = (int)((per_stage / 2 - (long long)pl.h_rows * 128) / (16 * 128));
+    if (fit >= 8 && fit < cap_units) cap_units = fit;
+  }
   if (nt_target >= 16 && nt_target / 16 < cap_units) cap_units = nt_target / 16;
   pl.tiles_per_cta = (u_max + cap_units - 1) / cap_units;
   // min_tiles > 1 cuts small per-CTA ranges into several tiles so that epilogues overlap the next
@@ -79,7 +113,6 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   // under ~16 KiB run into the per-thread TMA issue rate.
   if (pl.tiles_per_cta < min_tiles && u_max >= 4 * min_tiles) pl.tiles_per_cta = min_tiles;
   pl.q_units = (u_max + pl.tiles_per_cta - 1) / pl.tiles_per_cta;
-  pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
   // One thread sustains only about three TMA operations per microsecond, so short tiles fetch
   // several 64-column slabs of the hidden dimension per operation (a 3-D box), aiming at >= 40 KiB
   // of W per operation (measured: 52 KiB operations stream the Qwen head 4% faster than 26 KiB ones).  Needs D % 64 == 0 (a slab index must not run into the next row).
@@ -96,7 +129,8 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
     while (sk > 1 && min_stages * umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, sk) + fixed > (size_t)max_smem) --sk;
     pl.slabs = sk;
   }
-  const size_t sb = umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, pl.slabs);
+  const size_t sb = pl.tail1_units ? umma_stage_bytes_tail(pl.mt, pl.q_units, pl.h_rows, pl.slabs, pl.tail_slabs)
+                                   : umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, pl.slabs);
   int stages = stages_cap > 1 ? stages_cap : kUmmaMaxStages;
   if (stages > kUmmaMaxStages) stages = kUmmaMaxStages;
   while (stages > 2 && stages * sb + fixed > (size_t)max_smem) --stages;
@@ -106,25 +140,41 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
 }
 
 // The tile schedule of one CTA, recomputed identically by every warp role.
+struct TileInfo {
+  int v0;    // first vocabulary row
+  int nt;    // rows (0: nothing, skip)
+  int kind;  // 0 = big tile, 1 / 2 = first / second closing tile
+};
+
 struct TileWalk {
-  int u_next;    // first unit of the next tile
-  int base, extra, i;
-  __device__ __forceinline__ TileWalk(int units_total, int T) {
+  int u_next;  // first unit of the next tile
+  int base, extra, i, T, tail1, tail2;
+  __device__ __forceinline__ TileWalk(int units_total, int T_, int tail1_, int tail2_) {
     const int per = units_total / (int)gridDim.x, rem = units_total % (int)gridDim.x;
     const int c = blockIdx.x;
     const int u_cnt = per + (c < rem ? 1 : 0);
     u_next = c * per + min(c, rem);
-    base = u_cnt / T;
-    extra = u_cnt % T;
+    T = T_;
+    tail1 = tail1_;
+    tail2 = tail2_;
+    const int big = u_cnt - tail1 - tail2;  // the planner only enables closing tiles when big > 0
+    base = big / T;
+    extra = big % T;
     i = 0;
   }
-  // rows of tile i (0 when this CTA has fewer units than tiles) and its first vocabulary row
-  __device__ __forceinline__ void next(int& v0, int& nt) {
-    const int units = base + (i < extra ? 1 : 0);
-    v0 = u_next * 16;
-    nt = units * 16;
+  __device__ __forceinline__ int count() const { return T + (tail1 ? 1 : 0) + (tail2 ? 1 : 0); }
+  __device__ __forceinline__ TileInfo next() {
+    int units, kind = 0;
+    if (i < T) {
+      units = base + (i < extra ? 1 : 0);
+    } else {
+      kind = i - T + 1;
+      units = kind == 1 ? tail1 : tail2;
+    }
+    TileInfo t{u_next * 16, units * 16, kind};
     u_next += units;
     ++i;
+    return t;
   }
 };
 
@@ -275,16 +325,21 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 template <int MT>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
-                   const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
-                   const int units_total, const int q_units, const int h_rows, const int SK) {
+                   const __grid_constant__ CUtensorMap h_map, const __grid_constant__ CUtensorMap w_map_t1,
+                   const __grid_constant__ CUtensorMap w_map_t2, const __grid_constant__ CUtensorMap h_map_t,
+                   const SampleParams p, const int nt_cap, const int units_total, const int q_units,
+                   const int h_rows, const int SK, const int tail1, const int tail2, const int SKT) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
   // stage = [SK W slabs][MT x SK hidden-state slabs]; SK > 1 means the maps are 3-D (slab = dim 2)
-  const size_t w_slab_bytes = (size_t)q_units * 16 * 128, h_slab_bytes = (size_t)h_rows * 128;
-  const size_t w_tile_bytes = SK * w_slab_bytes, h_tile_bytes = SK * h_slab_bytes;
-  const size_t stage_bytes = w_tile_bytes + MT * h_tile_bytes;
+  // A stage holds `sk` W slabs of the tile (sk * nt * 128 bytes) followed at once by MT x sk
+  // hidden-state slabs; sk is SK for the big tiles and SKT for the closing tiles.
+  const size_t h_slab_bytes = (size_t)h_rows * 128;
+  const size_t stage_bytes = tail1 ? umma_stage_bytes_tail(MT, q_units, h_rows, SK, SKT)
+                                   : umma_stage_bytes(MT, q_units, h_rows, SK);
+  const int slabs_total = (p.D + kUmmaBK - 1) / kUmmaBK;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
   smem += 1024;  // stages start 1 KiB-aligned behind the barriers
   uint64_t* empty_bar = full_bar + stages;
@@ -295,7 +350,6 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int acc_stages = kTmemCols / (MT * nt_cap);
-  const int KB = ((p.D + kUmmaBK - 1) / kUmmaBK + SK - 1) / SK;  // pipeline steps per tile
 
   const int cta = blockIdx.x;
 
@@ -349,13 +403,20 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
       int it = 0;
       bool ok = true;
-      TileWalk walk(units_total, n_tiles);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        int v0, NT;
-        walk.next(v0, NT);
+      TileWalk walk(units_total, n_tiles, tail1, tail2);
+      const int total_tiles = walk.count();
+      for (int t = 0; t < total_tiles && ok; ++t) {
+        const TileInfo ti = walk.next();
+        const int v0 = ti.v0, NT = ti.nt;
         if (NT == 0) continue;
-        const uint32_t tx = (uint32_t)SK * (is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u);
-        const CUtensorMap* wm = (NT == q_units * 16) ? &w_map_q : &w_map_q1;
+        const int sk = ti.kind ? SKT : SK;
+        const int KB = (slabs_total + sk - 1) / sk;  // pipeline steps of this tile
+        const uint32_t tx = (uint32_t)sk * (is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u);
+        const CUtensorMap* wm = ti.kind == 0 ? ((NT == q_units * 16) ? &w_map_q : &w_map_q1)
+                                             : (ti.kind == 1 ? &w_map_t1 : &w_map_t2);
+        const CUtensorMap* hm = ti.kind == 0 ? &h_map : &h_map_t;
+        const bool flat = (SK == 1 && tail1 == 0);  // one slab per stage and no closing tiles: 2-D maps
+        const size_t h_off = (size_t)sk * NT * 128;   // hidden-state slabs follow the W slabs
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int st = it % stages;
           const uint32_t n = (uint32_t)(it / stages);
@@ -366,14 +427,14 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           uint8_t* sw = smem + st * stage_bytes;
           mbar_arrive_expect_tx(&full_bar[st], tx);
           if (is_w) {
-            if (SK == 1) tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
-            else tma_load_3d_hint(sw, wm, 0, v0, kb * SK, &full_bar[st], pol);
+            if (flat) tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
+            else tma_load_3d_hint(sw, wm, 0, v0, kb * sk, &full_bar[st], pol);
           } else {
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              uint8_t* dst = sw + w_tile_bytes + m * h_tile_bytes;
-              if (SK == 1) tma_load_2d_hint(dst, &h_map, kb * kUmmaBK, m * 128, &full_bar[st], pol);
-              else tma_load_3d_hint(dst, &h_map, 0, m * 128, kb * SK, &full_bar[st], pol);
+              uint8_t* dst = sw + h_off + (size_t)m * sk * h_slab_bytes;
+              if (flat) tma_load_2d_hint(dst, hm, kb * kUmmaBK, m * 128, &full_bar[st], pol);
+              else tma_load_3d_hint(dst, hm, 0, m * 128, kb * sk, &full_bar[st], pol);
             }
           }
         }
@@ -390,11 +451,15 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      TileWalk walk(units_total, n_tiles);
-      for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
-        int v0, NT;
-        walk.next(v0, NT);
+      TileWalk walk(units_total, n_tiles, tail1, tail2);
+      const int total_tiles = walk.count();
+      for (int t = 0, ta = 0; t < total_tiles && ok; ++t) {
+        const TileInfo ti = walk.next();
+        const int NT = ti.nt;
         if (NT == 0) continue;
+        const int sk = ti.kind ? SKT : SK;
+        const int KB = (slabs_total + sk - 1) / sk;
+        const uint32_t h_off = (uint32_t)(sk * NT * 128);
         const uint32_t idesc = umma_idesc(NT);
         const int j = ta % acc_stages;
         const uint32_t un = (uint32_t)(ta / acc_stages);
@@ -411,12 +476,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           tc_fence_after();
           if (it == 0) stamp(p, 2);
           const uint32_t sw = smem_u32(smem + st * stage_bytes);
-          for (int sl = 0; sl < SK; ++sl) {
+          for (int sl = 0; sl < sk; ++sl) {
             // TMA packs the slabs of a box back to back: the slab pitch follows the tile height
             const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)(sl * NT * 128));
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + m * h_tile_bytes + sl * h_slab_bytes));
+              const uint64_t adesc =
+                  umma_smem_desc(sw + h_off + (uint32_t)((m * sk + sl) * h_slab_bytes));
               const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
 #pragma unroll
               for (int k = 0; k < kUmmaBK / 16; ++k) {
@@ -463,10 +529,11 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
 
-    TileWalk walk(units_total, n_tiles);
-    for (int t = 0, ta = 0; t < n_tiles; ++t) {
-      int v0, NT;
-      walk.next(v0, NT);
+    TileWalk walk(units_total, n_tiles, tail1, tail2);
+    const int total_tiles = walk.count();
+    for (int t = 0, ta = 0; t < total_tiles; ++t) {
+      const TileInfo ti = walk.next();
+      const int v0 = ti.v0, NT = ti.nt;
       if (NT == 0) continue;
       // column range of this warp inside the tile: whole 32-column chunks, dealt out evenly
       const int chunks = (NT + 31) / 32;
@@ -478,7 +545,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       ++ta;
       if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
       tc_fence_after();
-      if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
+      if (ew == 0 && lane == 0 && t == total_tiles - 1) stamp(p, 4);
       if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         for (int s = 0; s < S; ++s) {

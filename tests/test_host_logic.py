@@ -57,9 +57,11 @@ def test_launch_plan_covers_the_vocabulary(lib, V, D, B):
             assert pl["tile_rows"] % 16 == 0 and 16 <= pl["tile_rows"] <= 256
             assert pl["m_tiles"] == (2 if B > 128 else 1)
             # balance: no CTA walks more than 16 rows beyond the average
-            busiest = pl["tiles_per_cta"] * pl["tile_rows"]
+            # the big tiles alone (closing tiles, if any, are two extra short ones) stay within one
+            # granule per tile of the even share
+            big_tiles = pl["tiles_per_cta"] - (2 if pl["tiles_per_cta"] > 2 and not pair and B <= 64 and D % 64 == 0 and V / pl["grid"] >= 24 * 16 else 0)
             workers = pl["grid"] // 2 if pair else pl["grid"]
-            assert busiest < V / workers + (32 if pair else 16) * (pl["tiles_per_cta"] + 1)
+            assert big_tiles * pl["tile_rows"] < V / workers + (32 if pair else 16) * (pl["tiles_per_cta"] + 1)
         else:
             assert B <= 8 and pl["tile_rows"] == (64 if 2 <= B <= 4 else 32) and pl["stages"] >= 3
 
