@@ -15,6 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfmms_b200.so"
 # status codes / flags (include/fmms_b200.h)
 OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(8)
 FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA, FLAG_TWO_STAGE = 1, 2, 4, 8, 16, 32
+FLAG_SEED_DEVICE = 64
 PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
 
 # every symbol the header declares: name -> (restype, argtypes)

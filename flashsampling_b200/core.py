@@ -86,7 +86,7 @@ def fused_mm_sample(
     hidden_states: torch.Tensor,  # [B, D] bf16
     num_samples: int,
     temperature: torch.Tensor,  # 0-d fp32 tensor on the device, or [B] for per-row temperatures
-    seed: int,
+    seed,  # int, or a 1-element int64 CUDA tensor that the kernel reads (replayable in CUDA graphs)
     greedy_sampling: bool = False,
     tp: TPInfo = TP1,
     return_logits: bool = False,
@@ -169,6 +169,13 @@ def fused_mm_sample(
         raise ValueError('kernel must be None, "gemv" or "mma"')
     if two_stage:
         flags |= _lib.FLAG_TWO_STAGE
+    if isinstance(seed, torch.Tensor):
+        if seed.device != dev or seed.dtype != torch.int64 or seed.numel() != 1:
+            raise ValueError("a tensor seed must be one int64 element on the weights' device")
+        flags |= _lib.FLAG_SEED_DEVICE
+        seed_arg = seed.data_ptr()
+    else:
+        seed_arg = int(seed) & 0xFFFFFFFFFFFFFFFF
 
     v_begin = 0
     if tp.size > 1:
@@ -188,7 +195,7 @@ def fused_mm_sample(
     status = _status_word(dev)
     common = (
         weights.data_ptr(), hidden_states.data_ptr(), temp_ptr, temp_stride, V, D, B, num_samples,
-        int(seed) & 0xFFFFFFFFFFFFFFFF, v_begin, flags, noise_ptr, noise_ld,
+        seed_arg, v_begin, flags, noise_ptr, noise_ld,
         logits.data_ptr() if logits is not None else None, out.data_ptr(),
         vals.data_ptr() if vals is not None else None, ws.data_ptr(), ws.numel(),
         status.data_ptr(), stream.cuda_stream,

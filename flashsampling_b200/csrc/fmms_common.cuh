@@ -15,7 +15,7 @@ namespace fmms {
 constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kErrWorkspace = 4,
               kErrCuda = 5, kErrArch = 6;
 constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
-              kFlagForceMma = 16, kFlagTwoStage = 32;
+              kFlagForceMma = 16, kFlagTwoStage = 32, kFlagSeedDev = 64;
 
 constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"
 
@@ -47,6 +47,13 @@ __device__ __forceinline__ uint4 noise_block(unsigned long long seed, int s, int
   const unsigned long long stream = seed + (unsigned long long)s;
   return philox4x32_10(make_uint4((uint32_t)v_quad, (uint32_t)b, (uint32_t)(v_quad >> 32), 0u),
                        make_uint2((uint32_t)stream, (uint32_t)(stream >> 32)));
+}
+
+// The seed of a call: the value itself, or (kFlagSeedDev) a uint64 read from device memory, so that
+// a launch captured in a CUDA graph draws fresh noise on every replay.
+__device__ __forceinline__ unsigned long long resolve_seed(unsigned long long seed_or_ptr, int flags) {
+  if (flags & kFlagSeedDev) return *reinterpret_cast<const volatile unsigned long long*>(seed_or_ptr);
+  return seed_or_ptr;
 }
 
 __device__ __forceinline__ float lg2_approx(float x) {

@@ -279,6 +279,7 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
   const bool ext = (p.flags & kFlagExtNoise) != 0;
   const bool ret_logits = (p.flags & kFlagReturnLogits) != 0;
   const int n_items = kGemvRowsPerWarp * NB * p.S;
+  const unsigned long long seed = resolve_seed(p.seed, p.flags);
 
   // Lane l owns the items i = j * 32 + l (j < kGemvItemsPerLane) of the warp's
   // rows_per_warp x NB x S results: row r = i % rows_per_warp, then b, then s.  Only the running
@@ -382,7 +383,7 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
             y = fmaf(val, 1.0f / temp, p.ext_noise[(size_t)item_s * p.noise_s_stride + (size_t)item_b * p.noise_ld + v]);
           } else {
             const unsigned long long vg = (unsigned long long)(p.v_offset + v);
-            const uint4 q = noise_block(p.seed, item_s, item_b + p.b_offset, vg >> 2);
+            const uint4 q = noise_block(seed, item_s, item_b + p.b_offset, vg >> 2);
             y = fmaf(val, 1.0f / temp, gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)));
           }
         }

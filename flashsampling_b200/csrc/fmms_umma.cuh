@@ -250,6 +250,7 @@ struct EpiRow {
   bool greedy, ext, ret_logits, quad_aligned;
   float inv_t;
   bool noisy;     // false for a row whose temperature is <= 0: that row is decoded greedily
+  unsigned long long seed;
 };
 
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
@@ -293,7 +294,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
         const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const uint4 q = noise_block(p.seed, s, e.b + p.b_offset, q0 + g);
+          const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {
@@ -309,7 +310,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
-          const uint4 q = noise_block(p.seed, s, e.b + p.b_offset, vg >> 2);
+          const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, vg >> 2);
           const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)) : 0.f);
           if (c + i < c_end && vbase + i < p.V && y > bv) {
             bv = y;
@@ -522,7 +523,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       noisy = temp > 0.f;  // temperature <= 0 selects greedy decoding for this row
       invT = noisy ? 1.0f / temp : 1.0f;
     }
-    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy};
+    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy, resolve_seed(p.seed, p.flags)};
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
 

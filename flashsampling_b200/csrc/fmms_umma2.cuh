@@ -302,7 +302,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
       invT = noisy ? 1.0f / temp : 1.0f;
     }
     const EpiRow row{b, row_ok, greedy, (p.flags & kFlagExtNoise) != 0, (p.flags & kFlagReturnLogits) != 0,
-                     (p.v_offset & 3) == 0, invT, noisy};
+                     (p.v_offset & 3) == 0, invT, noisy, resolve_seed(p.seed, p.flags)};
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
     float best_val = -INFINITY;

@@ -29,20 +29,32 @@ class SamplingMetadata:
 class FMMSSampler:
     """``sampler(lm_head_weight, hidden_states, metadata) -> int32 [num_requests]`` token ids."""
 
-    def __init__(self, seed: int = 0, tp: TPInfo = TP1):
+    def __init__(self, seed: int = 0, tp: TPInfo = TP1, device_seed: bool = False):
+        """``device_seed=True`` keeps the step's seed in a device tensor that is advanced by a tiny
+        device op before every call, so the whole call can be captured in a CUDA graph and still
+        draw fresh noise on every replay."""
         self.seed = int(seed)
         self.step = 0
         self.tp = tp
+        self.device_seed = device_seed
+        self._seed_t = None
 
     def __call__(self, lm_head_weight: torch.Tensor, hidden_states: torch.Tensor,
                  sampling_metadata: SamplingMetadata) -> torch.Tensor:
         self.step += 1
+        if self.device_seed:
+            if self._seed_t is None:
+                self._seed_t = torch.full((1,), self.seed, dtype=torch.int64, device=lm_head_weight.device)
+            self._seed_t += 1  # enqueued on the stream (captured with the call)
+            seed = self._seed_t
+        else:
+            seed = self.seed + self.step  # draw s of a call uses stream seed + s: one fresh stream per step
         ids = fused_mm_sample(
             weights=lm_head_weight,
             hidden_states=hidden_states,
             num_samples=1,
             temperature=sampling_metadata.temperature,
-            seed=self.seed + self.step,  # draw s of a call uses stream seed + s: one fresh stream per step
+            seed=seed,
             greedy_sampling=sampling_metadata.all_greedy,
             tp=self.tp,
         )

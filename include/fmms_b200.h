@@ -44,6 +44,9 @@ extern "C" {
 #define FMMS_FLAG_RETURN_LOGITS 4  /* also store fp32 logits (core.py RETURN_LOGITS, :568-573) */
 #define FMMS_FLAG_FORCE_GEMV 8     /* use the small-batch weight-streaming kernel              */
 #define FMMS_FLAG_FORCE_MMA 16     /* use the tcgen05 tensor-core kernel                       */
+#define FMMS_FLAG_SEED_DEVICE 64   /* `seed` is a DEVICE POINTER to a uint64 seed that the kernel reads:
+                                      a launch captured in a CUDA graph then draws fresh noise on every
+                                      replay once the caller advances the value between replays       */
 #define FMMS_FLAG_TWO_STAGE 32     /* decode the winners in a second kernel (the reference's
                                       stage 2, core.py:359-370) instead of the last CTA        */
 

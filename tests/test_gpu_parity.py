@@ -291,6 +291,33 @@ def test_step_replays_inside_a_cuda_graph(fs, kernel, B):
     fs.check_status()
 
 
+def test_device_seed_gives_fresh_draws_on_graph_replay(fs):
+    """FMMS_FLAG_SEED_DEVICE: the seed is read from device memory, so a captured step draws new noise
+    on every replay; each replay equals the eager call with that seed."""
+    V, D, B = 20000, 256, 24
+    w, h = _head(V, D, B, w_std=0.08, seed=8)
+    w, h = w.to(_dev()), h.to(_dev())
+    t = torch.tensor(1.0, device=_dev())
+    seed_t = torch.tensor([100], dtype=torch.int64, device=_dev())
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fs.fused_mm_sample(w, h, 1, t, seed=seed_t)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        seed_t += 1
+        captured = fs.fused_mm_sample(w, h, 1, t, seed=seed_t)
+    seen = []
+    for k in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        want = fs.fused_mm_sample(w, h, 1, t, seed=int(seed_t.item()))
+        assert torch.equal(captured, want)
+        seen.append(captured.clone())
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
+    fs.check_status()
+
+
 def test_argument_errors(fs):
     w = torch.zeros(64, 16, dtype=torch.bfloat16, device=_dev())
     h = torch.zeros(2, 24, dtype=torch.bfloat16, device=_dev())
