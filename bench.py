@@ -362,7 +362,7 @@ def run_b200(args):
     tflops_peak = measured_tensor_peak()
     tensor_bound = flops / (tflops_peak * 1e12) > algorithmic_bytes(v_local, D, B, S) / (peak * 1e9)
     traffic = None
-    tfile = ROOT / "profiles" / "traffic.json"
+    tfile = ROOT / "profiles" / "dram_traffic_per_launch.txt"
     if tfile.exists():
         traffic = json.loads(tfile.read_text()).get(f"{args.workload}_B{B}_N{world}")
     line = {
