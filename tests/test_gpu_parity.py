@@ -90,10 +90,10 @@ def test_greedy_is_argmax(fs, kernel, V, nh):
 
 GEMV_SHAPES = [  # V, D, B, S
     (100, 16, 1, 1), (129, 72, 2, 3), (1000, 256, 3, 2), (4097, 520, 4, 1), (5000, 1024, 5, 1),
-    (6151, 264, 8, 4), (33, 8, 7, 1), (20000, 4096, 4, 2), (18992, 4096, 1, 1), (9000, 768, 5, 1),
+    (6151, 264, 8, 4), (33, 8, 7, 1), (20000, 4096, 4, 2), (18992, 4096, 1, 1), (9000, 768, 5, 1), (5, 8, 3, 2),
 ]
 MMA_SHAPES = [
-    (100, 16, 1, 1), (129, 72, 2, 3), (1000, 256, 15, 2), (4097, 520, 16, 1), (5000, 1024, 17, 1),
+    (5, 8, 3, 2), (100, 16, 1, 1), (129, 72, 2, 3), (1000, 256, 15, 2), (4097, 520, 16, 1), (5000, 1024, 17, 1),
     (6151, 264, 63, 2), (3000, 64, 64, 1), (2049, 128, 65, 1), (33, 8, 128, 1), (4500, 200, 129, 2),
     (9000, 512, 256, 1), (70000, 320, 33, 1), (50000, 4096, 8, 1),
     (3000, 64, 300, 2), (2000, 128, 513, 1),  # more than 256 rows: consecutive launches over blocks of 256 rows
@@ -163,7 +163,7 @@ def test_vocab_offset_shifts_ids_and_noise(fs):
     logits = O.logits_fp32(w, h)
     for kernel, flag in (("gemv", _lib.FLAG_FORCE_GEMV), ("mma", _lib.FLAG_FORCE_MMA)):
         best_v, best_i = None, None
-        for lo, hi in ((0, 1024), (1024, 4096)):
+        for lo, hi in ((0, 1001), (1001, 2048), (2048, 4096)):  # 1001: a block that does not start on a multiple of 4
             ws = w[lo:hi].contiguous().to(_dev())
             out = torch.empty((B, S), dtype=torch.int64, device=_dev())
             val = torch.empty((B, S), dtype=torch.float32, device=_dev())
@@ -184,6 +184,7 @@ def test_vocab_offset_shifts_ids_and_noise(fs):
             else:
                 take = val.cpu() > best_v
                 best_i = torch.where(take, out.cpu(), best_i)
+                best_v = torch.where(take, val.cpu(), best_v)
         _check_indices(best_i, logits, 0.8, noise, f"sharded {kernel}")
 
 
