@@ -88,6 +88,23 @@ def test_greedy_is_argmax(fs, kernel, V, nh):
     fs.check_status()
 
 
+@pytest.mark.parametrize("V,D", [(128, 264), (129, 264), (512, 72), (262208, 64)])
+def test_greedy_and_logits_over_ragged_batches(fs, V, D):
+    """Deterministic modes over the ragged grid of batch sizes (one below, at and above every tile and
+    kernel boundary) and vocabularies (128, 129, 512, and 262208 = 2048 * 128 + 64)."""
+    for B in (1, 2, 3, 15, 16, 17, 63, 64, 65, 128, 129, 256):
+        w, h = _head(V, D, B, w_std=1.0 / np.sqrt(D), seed=B)
+        ref = O.logits_fp32(w, h)
+        ids, logits = fs.fused_mm_sample(w.to(_dev()), h.to(_dev()), 1, torch.empty((), device=_dev()), seed=0,
+                                         greedy_sampling=True, return_logits=True)
+        torch.testing.assert_close(logits.cpu(), ref, atol=1e-4, rtol=1e-4)
+        top2 = ref.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 1e-3 * top2[:, 0].abs()
+        assert clear.float().mean() > 0.9
+        assert torch.equal(ids.cpu()[clear, 0], ref.argmax(-1)[clear]), (V, D, B)
+    fs.check_status()
+
+
 GEMV_SHAPES = [  # V, D, B, S
     (100, 16, 1, 1), (129, 72, 2, 3), (1000, 256, 3, 2), (4097, 520, 4, 1), (5000, 1024, 5, 1),
     (6151, 264, 8, 4), (33, 8, 7, 1), (20000, 4096, 4, 2), (18992, 4096, 1, 1), (9000, 768, 5, 1), (5, 8, 3, 2),
