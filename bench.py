@@ -303,6 +303,15 @@ def run_b200(args):
             remeasured = True
         res = dict(B=B, path=path, times_ms=times, ref_times_ms=ref_times, wall_s=wall, clocks=clk.summary(),
                    clocks_region=clk_region.summary(), n_copies=n_copies, region_ms=region_ms, region_kind=region_kind, remeasured=remeasured)
+        if with_e2e and world == 1:
+            # the same step with the optional log-probability output (running log-sum-exp in the epilogue)
+            def logprob_step():
+                seed[0] += S
+                turn[0] += 1
+                return fs.fused_mm_sample(ws[turn[0] % n_copies], h, S, t, seed=seed[0], return_logprobs=True)
+
+            logprob_step()
+            res["logprob_times_ms"], _ = time_steps(logprob_step, max(10, steps // 4), 3, sweep_read, barrier)
         if with_e2e:
             h_host = h.cpu().pin_memory()
             t_host = t.cpu().pin_memory()
@@ -398,6 +407,8 @@ def run_b200(args):
         "write_flush_protocol_note": "the reference's protocol: a 256 MB buffer is zeroed before each timed call; its "
                                      "dirty lines are written back during the timed kernel",
         "clocks": main["clocks"] if main["clocks"]["samples"] else main["clocks_region"],
+        **({"with_logprobs_us": round(statistics.median(main["logprob_times_ms"]) * 1e3, 3)}
+           if "logprob_times_ms" in main else {}),
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",

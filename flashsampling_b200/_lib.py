@@ -16,6 +16,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfmms_b200.so"
 OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(8)
 FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA, FLAG_TWO_STAGE = 1, 2, 4, 8, 16, 32
 FLAG_SEED_DEVICE = 64
+FLAG_LOGPROB = 128
 PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
 
 # every symbol the header declares: name -> (restype, argtypes)
@@ -55,6 +56,14 @@ SIGNATURES = {
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_longlong, c_int,
             c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
             c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.c_uint, c_ulonglong,
+        ],
+    ),
+    "fmms_sample_logprobs": (
+        c_int,
+        [
+            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_longlong, c_int,
+            c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
+            c_void_p, c_void_p,  # out_logprob, out_lse
         ],
     ),
     "fmms_last_path": (c_int, []),

@@ -95,13 +95,17 @@ def fused_mm_sample(
     kernel: str | None = None,  # None = automatic, "gemv" or "mma" forces a kernel
     return_values: bool = False,
     two_stage: bool = False,  # decode the winners in a second kernel instead of the last CTA
+    return_logprobs: bool = False,  # also return ln p(sampled id) [B, num_samples] from the same pass
 ):
     """Sample ``num_samples`` token ids per hidden-state row from softmax(W h / T).
 
     Arguments follow core.py:224-234.  Extensions: ``temperature`` may hold one
     value per row; ``noise`` supplies the Gumbel noise (parity checks);
     ``kernel`` pins the kernel; ``return_values`` also returns the winning
-    perturbed logits ``[B, num_samples]``.  ``p2p_no_overlap`` selects the
+    perturbed logits ``[B, num_samples]``; ``return_logprobs`` also returns the
+    log-probability of every sampled id under softmax(W h / T) (fp32
+    ``[B, num_samples]``; T = 1 for greedy rows), computed by the same pass
+    from a running log-sum-exp.  ``p2p_no_overlap`` selects the
     reference's ablation in which the exchange follows the kernel; here the
     exchange always follows the local reduction, so the flag changes nothing.
 
@@ -168,6 +172,8 @@ def fused_mm_sample(
     elif kernel is not None:
         raise ValueError('kernel must be None, "gemv" or "mma"')
     if two_stage:
+        if return_logprobs:
+            raise ValueError("return_logprobs is not available with two_stage")
         flags |= _lib.FLAG_TWO_STAGE
     if isinstance(seed, torch.Tensor):
         if seed.device != dev or seed.dtype != torch.int64 or seed.numel() != 1:
@@ -186,6 +192,10 @@ def fused_mm_sample(
     out = torch.empty((B, num_samples), dtype=torch.int64, device=dev)
     need_vals = return_values or tp.size > 1
     vals = torch.empty((B, num_samples), dtype=torch.float32, device=dev) if need_vals else None
+    logprobs = lse = None
+    if return_logprobs:
+        logprobs = torch.empty((B, num_samples), dtype=torch.float32, device=dev)
+        lse = torch.empty((B,), dtype=torch.float32, device=dev)
 
     stream = torch.cuda.current_stream(dev)
     nbytes = _ws_bytes.get((B, num_samples))
@@ -201,9 +211,12 @@ def fused_mm_sample(
         status.data_ptr(), stream.cuda_stream,
     )
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
-        and not two_stage and B <= 256  # larger batches run as several launches, then one exchange
+        and not two_stage and B <= 256 \
+        and not return_logprobs  # larger batches run as several launches, then one exchange
     with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
-        if fused_tp:
+        if return_logprobs:
+            rc = lib.fmms_sample_logprobs(*common, logprobs.data_ptr(), lse.data_ptr())
+        elif fused_tp:
             # one launch: the sampling kernel's last CTA runs the NVLink exchange itself
             rc = lib.fmms_sample_tp(*common, tp.rank, tp.size, exchange.max_items, exchange.ptrs,
                                     exchange.next_epoch(), 0)
@@ -211,7 +224,13 @@ def fused_mm_sample(
             rc = lib.fmms_sample(*common)
     _lib.check(rc, "fmms_sample_tp" if fused_tp else "fmms_sample")
 
-    if tp.size > 1 and not fused_tp:
+    if tp.size > 1 and return_logprobs:
+        # every rank holds its shard's winner, that winner's log-probability under the shard's
+        # own normaliser, and the normaliser: gather all three and renormalise
+        from .tensor_parallel import reduce_gathered_logprobs
+
+        out, vals, logprobs = reduce_gathered_logprobs(exchange, out, vals, logprobs, lse)
+    elif tp.size > 1 and not fused_tp:
         out, vals = exchange.reduce(out, vals)
 
     result = (out,)
@@ -219,6 +238,8 @@ def fused_mm_sample(
         result += (logits,)
     if return_values:
         result += (vals,)
+    if return_logprobs:
+        result += (logprobs,)
     return result[0] if len(result) == 1 else result
 
 

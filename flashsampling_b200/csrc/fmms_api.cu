@@ -31,8 +31,8 @@ struct DeviceInfo {
   int num_sms = 0;
   int cc_major = 0;
   int max_smem_optin = 0;
-  bool gemv_attr[kGemvMaxBatch + 1] = {};
-  bool umma_attr[8] = {};
+  bool gemv_attr[2][kGemvMaxBatch + 1] = {};  // [with log-probabilities][batch rows]
+  bool umma_attr[2][8] = {};
 };
 
 static std::mutex g_mu;
@@ -127,13 +127,19 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, int b
 }
 
 // Workspace layout, a function of the workspace SIZE only (so calls of different shapes that
-// share one workspace agree on it): [ticket: 256 B][keys: cap u64][running candidates:
-// kMaxParts * cap * (f32 + i32)], cap = the number of (row, draw) items the size can hold.
-// Ticket and keys must be zero when a call starts; every call leaves them zero again.
+// share one workspace agree on it): [ticket: 256 B][log-sum-exp slots: 256 u64][keys: cap u64]
+// [running candidates: kMaxParts * cap * (f32 + i32)], cap = the number of (row, draw) items the
+// size can hold.  Ticket, slots and keys must be zero when a call starts; every call leaves them
+// zero again.
+constexpr int kMaxBatchPerLaunch = 256;
+constexpr size_t kWsLseOffset = 256;
+constexpr size_t kWsHeadBytes = kWsLseOffset + (size_t)kMaxBatchPerLaunch * 8;
 static size_t workspace_bytes_for(int B, int S) {
-  return 256 + (size_t)B * (size_t)S * 8 * (1 + (size_t)kMaxParts);
+  return kWsHeadBytes + (size_t)B * (size_t)S * 8 * (1 + (size_t)kMaxParts);
 }
-static size_t workspace_item_capacity(size_t bytes) { return (bytes - 256) / (8 * (1 + (size_t)kMaxParts)); }
+static size_t workspace_item_capacity(size_t bytes) {
+  return (bytes - kWsHeadBytes) / (8 * (1 + (size_t)kMaxParts));
+}
 
 // [rows, cols] bf16 matrix seen as (inner columns, rows, cols / inner groups); box = inner x box_rows x groups.
 static int get_tensor_map_3d(const void* ptr, long long rows, long long cols, int inner, int box_rows, int slabs,
@@ -176,17 +182,26 @@ static int get_tensor_map_chunks(const void* ptr, long long rows, long long cols
 }
 
 // ---- GEMV launch ----------------------------------------------------------------
+template <int NB, bool LSE>
+static int launch_gemv_nb_lse(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
+                              cudaStream_t stream) {
+  if (!d.gemv_attr[LSE][NB]) {
+    if (cudaFuncSetAttribute(gemv_sample_kernel<NB, LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             d.max_smem_optin) != cudaSuccess)
+      return kErrCuda;
+    d.gemv_attr[LSE][NB] = true;
+  }
+  gemv_sample_kernel<NB, LSE><<<grid, kGemvThreads, smem, stream>>>(map, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+// The kernels that also accumulate the log-sum-exp (kFlagLogprob) are separate instantiations,
+// so that the plain sampling kernels carry none of that code.
 template <int NB>
 static int launch_gemv_nb(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
                           cudaStream_t stream) {
-  if (!d.gemv_attr[NB]) {
-    if (cudaFuncSetAttribute(gemv_sample_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             d.max_smem_optin) != cudaSuccess)
-      return kErrCuda;
-    d.gemv_attr[NB] = true;
-  }
-  gemv_sample_kernel<NB><<<grid, kGemvThreads, smem, stream>>>(map, p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+  return (p.flags & kFlagLogprob) ? launch_gemv_nb_lse<NB, true>(d, map, p, grid, smem, stream)
+                                  : launch_gemv_nb_lse<NB, false>(d, map, p, grid, smem, stream);
 }
 
 // Tuning knobs (read once): FMMS_GEMV_STAGES / FMMS_UMMA_STAGES cap the shared-memory ring depth.
@@ -270,19 +285,26 @@ struct UmmaMaps {
   CUtensorMap wq, wq1, hm, wt1, wt2, hmt;
 };
 
-template <int MT>
-static int launch_umma_mt(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
-                          cudaStream_t stream) {
-  if (!d.umma_attr[MT]) {
-    if (cudaFuncSetAttribute(umma_sample_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+template <int MT, bool LSE>
+static int launch_umma_mt_lse(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
+                              cudaStream_t stream) {
+  if (!d.umma_attr[LSE][MT]) {
+    if (cudaFuncSetAttribute(umma_sample_kernel<MT, LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              d.max_smem_optin) != cudaSuccess)
       return kErrCuda;
-    d.umma_attr[MT] = true;
+    d.umma_attr[LSE][MT] = true;
   }
-  umma_sample_kernel<MT><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
+  umma_sample_kernel<MT, LSE><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
       mp.wq, mp.wq1, mp.hm, mp.wt1, mp.wt2, mp.hmt, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs,
       pl.tail1_units, pl.tail2_units, pl.tail_slabs);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+template <int MT>
+static int launch_umma_mt(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
+                          cudaStream_t stream) {
+  return (p.flags & kFlagLogprob) ? launch_umma_mt_lse<MT, true>(d, mp, p, pl, stream)
+                                  : launch_umma_mt_lse<MT, false>(d, mp, p, pl, stream);
 }
 
 static int umma_slabs_force() {
@@ -379,17 +401,22 @@ static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleP
   }
   rc = get_tensor_map_slabs(H, p.B, p.D, 128, pl.slabs, &hm);
   if (rc != kOk) return -rc;
-  if (!d.umma_attr[3]) {
-    if (cudaFuncSetAttribute(umma_pair_sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             d.max_smem_optin) != cudaSuccess)
+  const bool lse = (p.flags & kFlagLogprob) != 0;
+  if (!d.umma_attr[lse][3]) {
+    if (cudaFuncSetAttribute(lse ? umma_pair_sample_kernel<true> : umma_pair_sample_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin) != cudaSuccess)
       return -kErrCuda;
-    d.umma_attr[3] = true;
+    d.umma_attr[lse][3] = true;
   }
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * kPairUnitRows;
   p.tiles_per_cta = pl.tiles_per_pair;
-  umma_pair_sample_kernel<<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total, pl.q_units,
-                                                                      pl.slabs);
+  if (lse)
+    umma_pair_sample_kernel<true><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total,
+                                                                              pl.q_units, pl.slabs);
+  else
+    umma_pair_sample_kernel<false><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total,
+                                                                               pl.q_units, pl.slabs);
   if (cudaGetLastError() != cudaSuccess) return -kErrCuda;
   return pl.grid * kUmmaEpiGroups;
 }
@@ -412,7 +439,7 @@ __global__ void l2_sweep_kernel(const uint4* __restrict__ p, size_t n16, unsigne
 // kStaticMaxItems (batch rows x draws) entries, 8 bytes each.  Every GPU on which the
 // library's module is loaded holds these bytes until the process exits.
 constexpr int kStaticMaxItems = 1024;
-constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxItems * 8 * (1 + (size_t)kMaxParts);
+constexpr size_t kStaticScratchBytes = kWsHeadBytes + (size_t)kStaticMaxItems * 8 * (1 + (size_t)kMaxParts);
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address;
@@ -524,14 +551,13 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
   return FMMS_OK;
 }
 
-constexpr int kMaxBatchPerLaunch = 256;
-
 struct TpArgs;
 static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                        int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
-                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa);
+                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
+                       float* out_logprob, float* out_lse);
 
 struct TpArgs {
   int rank, world, max_items;
@@ -544,7 +570,8 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                        int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
                        int flags, const float* ext_noise, long long noise_ld, float* logits_out,
                        long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
-                       int* status_dev, void* stream_v, const TpArgs* tpa) {
+                       int* status_dev, void* stream_v, const TpArgs* tpa, float* out_logprob = nullptr,
+                       float* out_lse = nullptr) {
   g_last_path = FMMS_PATH_NONE;
   if (!W_bf16 || !H_bf16 || !out_idx || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
   const bool greedy = flags & FMMS_FLAG_GREEDY, ext = flags & FMMS_FLAG_EXT_NOISE;
@@ -554,6 +581,11 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
   if ((flags & FMMS_FLAG_RETURN_LOGITS) && !logits_out) return FMMS_ERR_BAD_ARG;
   if ((flags & FMMS_FLAG_FORCE_GEMV) && (flags & FMMS_FLAG_FORCE_MMA)) return FMMS_ERR_BAD_ARG;
   if (v_global_offset < 0) return FMMS_ERR_BAD_ARG;
+  if (flags & FMMS_FLAG_LOGPROB) {
+    if (!out_logprob) return FMMS_ERR_BAD_ARG;
+    // the log-sum-exp is merged on one GPU and decoded by the last CTA
+    if (tpa || (flags & FMMS_FLAG_TWO_STAGE)) return FMMS_ERR_UNSUPPORTED;
+  }
   if (D % 8 != 0 || ((uintptr_t)W_bf16 & 15) || ((uintptr_t)H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
   if (B > kMaxBatchPerLaunch) {
     // Larger batches run as consecutive launches over blocks of 256 rows (each streams W again,
@@ -567,21 +599,24 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                                  ext_noise ? ext_noise + (size_t)b0 * noise_ld : nullptr, noise_ld,
                                  (long long)B * noise_ld, b0, logits_out ? logits_out + (size_t)b0 * V_local : nullptr,
                                  out_idx + (size_t)b0 * S, out_val ? out_val + (size_t)b0 * S : nullptr, workspace,
-                                 workspace_bytes, status_dev, stream_v, nullptr);
+                                 workspace_bytes, status_dev, stream_v, nullptr,
+                                 out_logprob ? out_logprob + (size_t)b0 * S : nullptr,
+                                 out_lse ? out_lse + b0 : nullptr);
       if (rc != FMMS_OK) return rc;
     }
     return FMMS_OK;
   }
   return sample_rows(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
                      ext_noise, noise_ld, (long long)B * noise_ld, 0, logits_out, out_idx, out_val, workspace,
-                     workspace_bytes, status_dev, stream_v, tpa);
+                     workspace_bytes, status_dev, stream_v, tpa, out_logprob, out_lse);
 }
 
 static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                        int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
-                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa) {
+                       size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
+                       float* out_logprob, float* out_lse) {
   const bool greedy = flags & FMMS_FLAG_GREEDY;
   (void)greedy;
   size_t need = 0;
@@ -614,8 +649,11 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
   const size_t cap = workspace_item_capacity(workspace_bytes);
   p.ticket = reinterpret_cast<unsigned int*>(ws);
   p.sched = p.ticket + 1;
-  p.keys = reinterpret_cast<unsigned long long*>(ws + 256);
-  p.cand_val = reinterpret_cast<float*>(ws + 256 + cap * 8);
+  p.lse = reinterpret_cast<unsigned long long*>(ws + kWsLseOffset);
+  p.out_logprob = out_logprob;
+  p.out_lse = out_lse;
+  p.keys = reinterpret_cast<unsigned long long*>(ws + kWsHeadBytes);
+  p.cand_val = reinterpret_cast<float*>(ws + kWsHeadBytes + cap * 8);
   p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
   p.out_idx = out_idx;
   p.out_val = out_val;
@@ -692,7 +730,15 @@ int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperat
                      ext_noise, noise_ld, logits_out, out_idx, out_val, workspace, workspace_bytes, status_dev,
                      stream, &tpa);
 }
-
+int fmms_sample_logprobs(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                         int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,
+                         int flags, const float* ext_noise, long long noise_ld, float* logits_out,
+                         long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                         int* status_dev, void* stream, float* out_logprob, float* out_lse) {
+  return sample_impl(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset,
+                     flags | FMMS_FLAG_LOGPROB, ext_noise, noise_ld, logits_out, out_idx, out_val, workspace,
+                     workspace_bytes, status_dev, stream, nullptr, out_logprob, out_lse);
+}
 
 // ---- tensor-parallel exchange -----------------------------------------------------------
 int fmms_tp_buffer_bytes(int world, int max_items, size_t* bytes) {

@@ -15,7 +15,7 @@ namespace fmms {
 constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kErrWorkspace = 4,
               kErrCuda = 5, kErrArch = 6;
 constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
-              kFlagForceMma = 16, kFlagTwoStage = 32, kFlagSeedDev = 64;
+              kFlagForceMma = 16, kFlagTwoStage = 32, kFlagSeedDev = 64, kFlagLogprob = 128;
 
 constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"
 
@@ -120,6 +120,60 @@ __device__ __forceinline__ void cand_key_decode(unsigned long long k, float& v, 
   b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
   v = __uint_as_float(b);
   idx = (int)(~(uint32_t)k);
+}
+
+// ------------------------------------------------------------------------------------
+// Running log-sum-exp of one batch row (kFlagLogprob), in base-2 units: the pair (m, l) stands
+// for l * 2^m with l = sum_v 2^(x_v * log2(e) - m); l == 0 means "nothing accumulated yet".
+// ------------------------------------------------------------------------------------
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2f = 0.6931471805599453f;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// (m, l) <- (m, l) + (m2, l2)
+__device__ __forceinline__ void lse_merge(float& m, float& l, float m2, float l2) {
+  if (!(l2 > 0.f)) return;
+  if (!(l > 0.f)) {
+    m = m2;
+    l = l2;
+    return;
+  }
+  const float mn = fmaxf(m, m2);
+  l = l * ex2_approx(m - mn) + l2 * ex2_approx(m2 - mn);
+  m = mn;
+}
+
+// Fold one scaled logit x2 = logit / T * log2(e) into (m, l); m starts at -inf, l at 0.
+__device__ __forceinline__ void lse_push(float& m, float& l, float x2) {
+  const float mn = fmaxf(m, x2);
+  l = l * ex2_approx(m - mn) + ex2_approx(x2 - mn);
+  m = mn;
+}
+
+// Merge a partial sum into the row's 64-bit slot (m in the high word, l in the low word; zero =
+// empty) with a compare-and-swap loop: every failed attempt means another partial got in.
+__device__ __forceinline__ void lse_atomic_merge(unsigned long long* slot, float m, float l) {
+  if (!(l > 0.f)) return;
+  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(slot);
+  for (int tries = 0; tries < (1 << 20); ++tries) {  // at most one retry per competing partial
+    float mn = __uint_as_float((uint32_t)(old >> 32)), ln = __uint_as_float((uint32_t)old);
+    lse_merge(mn, ln, m, l);
+    const unsigned long long neu = ((unsigned long long)__float_as_uint(mn) << 32) | __float_as_uint(ln);
+    const unsigned long long prev = atomicCAS(slot, old, neu);
+    if (prev == old) break;
+    old = prev;
+  }
+}
+
+// Natural-log normaliser ln(sum_v exp(logit_v / T)) from a slot's bits.
+__device__ __forceinline__ float lse_value(unsigned long long bits) {
+  const float m = __uint_as_float((uint32_t)(bits >> 32)), l = __uint_as_float((uint32_t)bits);
+  return (m + log2f(l)) * kLn2f;
 }
 
 // ------------------------------------------------------------------------------------

@@ -53,6 +53,10 @@ struct SampleParams {
   int* cand_idx;
   long long* out_idx;        // [B, S]
   float* out_val;            // [B, S] or null
+  // kFlagLogprob: per-row log-sum-exp slots (zero on entry and on exit) and the outputs
+  unsigned long long* lse;   // [B] packed (m, l)
+  float* out_logprob;        // [B, S] ln p(sampled id)
+  float* out_lse;            // [B] ln sum_v exp(logit_v / T), or null
   int* status_dev;
   unsigned long long* stamps;  // optional [gridDim.x][8] %globaltimer stamps of the kernel's phases (null = off)
   int stages;                // shared-memory ring depth
@@ -73,7 +77,25 @@ __device__ __forceinline__ void stamp(const SampleParams& p, int slot) {
   if (p.stamps) p.stamps[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
 }
 
-template <class SyncFn>
+// Log-probability of a decoded winner (kFlagLogprob): the perturbed value minus the winner's
+// own noise, which is a pure function of (seed, draw, row, id), gives logit / T; the row's
+// log-sum-exp slot gives the normaliser.
+__device__ __forceinline__ float winner_logprob(const SampleParams& p, int b, int s, float y, int idx, float lse) {
+  if (idx < 0 || idx >= p.V) return __int_as_float(0x7fc00000);  // no candidate: NaN
+  float g = 0.f;
+  if (!(p.flags & kFlagGreedy) && p.temperature[(size_t)b * p.temp_stride] > 0.f) {
+    if (p.flags & kFlagExtNoise) {
+      g = p.ext_noise[(size_t)s * p.noise_s_stride + (size_t)b * p.noise_ld + idx];
+    } else {
+      const unsigned long long vg = (unsigned long long)(p.v_offset + idx);
+      const uint4 q = noise_block(resolve_seed(p.seed, p.flags), s, b + p.b_offset, vg >> 2);
+      g = gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u));
+    }
+  }
+  return (y - g) - lse;
+}
+
+template <bool LSE = false, class SyncFn>
 __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, int nthreads, SyncFn sync,
                                               volatile int* is_last, bool fenced_and_synced = false) {
   if (!fenced_and_synced) {
@@ -95,6 +117,15 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
       const int s = item / p.B, b = item - s * p.B;
       p.out_idx[(size_t)b * p.S + s] = p.v_offset + idx;
       if (p.out_val) p.out_val[(size_t)b * p.S + s] = v;
+      if constexpr (LSE) {
+        const float lse = lse_value(*reinterpret_cast<volatile unsigned long long*>(&p.lse[b]));
+        p.out_logprob[(size_t)b * p.S + s] = winner_logprob(p, b, s, v, idx, lse);
+        if (s == 0 && p.out_lse) p.out_lse[b] = lse;
+      }
+    }
+    if constexpr (LSE) {
+      sync();  // every draw of a row has read the row's slot
+      for (int b = tid; b < p.B; b += nthreads) p.lse[b] = 0ull;
     }
     if (tid == 0) {
       *p.ticket = 0u;
@@ -155,7 +186,7 @@ __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t x) {
   return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
 }
 
-template <int NB>
+template <int NB, bool LSE = false>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -291,6 +322,15 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     best_val[j] = -INFINITY;
     best_idx[j] = kIdxNone;
   }
+  // kFlagLogprob: running log-sum-exp of the items of draw 0 (one per vocabulary row and batch row)
+  float lse_m[LSE ? kGemvItemsPerLane : 1], lse_l[LSE ? kGemvItemsPerLane : 1];
+  if constexpr (LSE) {
+#pragma unroll
+    for (int j = 0; j < kGemvItemsPerLane; ++j) {
+      lse_m[j] = -INFINITY;
+      lse_l[j] = 0.f;
+    }
+  }
 
   int it = 0;
   for (;;) {
@@ -375,8 +415,12 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
         float y;
         if (greedy) {
           y = val;
+          if constexpr (LSE)
+            if (item_s == 0) lse_push(lse_m[j], lse_l[j], val * kLog2e);
         } else {
           const float temp = p.temperature[(size_t)item_b * p.temp_stride];
+          if constexpr (LSE)
+            if (item_s == 0) lse_push(lse_m[j], lse_l[j], val * ((temp > 0.f ? 1.0f / temp : 1.0f) * kLog2e));
           if (temp <= 0.f) {
             y = val;  // temperature <= 0 selects greedy decoding for this row
           } else if (ext) {
@@ -424,9 +468,38 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     const int b = tid % NB, s = tid / NB;
     if (b < p.B && bi != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(bv, bi));
   }
+  if constexpr (LSE) {
+    // the same two steps for the log-sum-exp of draw 0: rows of a warp by shuffles, then warps
+#pragma unroll
+    for (int j = 0; j < kGemvItemsPerLane; ++j) {
+#pragma unroll
+      for (int off = 1; off < kGemvRowsPerWarp; off <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, lse_m[j], off);
+        const float l2 = __shfl_xor_sync(0xffffffffu, lse_l[j], off);
+        lse_merge(lse_m[j], lse_l[j], m2, l2);
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory");  // red_* have been read
+    float* red_l = reinterpret_cast<float*>(red_idx);
+#pragma unroll
+    for (int j = 0; j < kGemvItemsPerLane; ++j) {
+      const int i = j * 32 + lane;
+      if ((i & (kGemvRowsPerWarp - 1)) == 0 && (i >> kRowShift) < NB) {  // slots of draw 0: slot = b
+        red_val[warp * 32 + (i >> kRowShift)] = lse_m[j];
+        red_l[warp * 32 + (i >> kRowShift)] = lse_l[j];
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory");
+    if (tid < NB && tid < p.B) {
+      float m = red_val[tid], l = red_l[tid];
+#pragma unroll
+      for (int w = 1; w < kGemvConsumerWarps; ++w) lse_merge(m, l, red_val[w * 32 + tid], red_l[w * 32 + tid]);
+      lse_atomic_merge(&p.lse[tid], m, l);
+    }
+  }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample(
+    finish_sample<LSE>(
         p, tid, kGemvConsumerWarps * 32,
         [] { asm volatile("bar.sync 1, %0;" ::"r"(kGemvConsumerWarps * 32) : "memory"); }, is_last);
   }

@@ -256,13 +256,35 @@ struct EpiRow {
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
 // quadrant, first column of the tile) for draw `s`: scale, add noise, keep the running (max, id)
 // of the thread's row.  The tile's first column is vocabulary row v0 of this shard.
+// With LSE, draw 0 also folds the scaled logits of the columns into the thread's running
+// log-sum-exp (lse_m, lse_l): one maximum and one rescale per 32-column chunk.
+template <bool LSE = false>
 __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
-                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
+                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi,
+                                                  float* lse_m = nullptr, float* lse_l = nullptr) {
   for (int c = c_begin; c < c_end; c += 32) {
     uint32_t acc[32];
     tmem_ld32(t_addr + (uint32_t)c, acc);
     if (e.row_ok) {
       const int vbase = v0 + c;
+      if constexpr (LSE) {
+        if (s == 0) {
+          const float sc = e.inv_t * kLog2e;
+          float mx = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c + i < c_end && vbase + i < p.V) mx = fmaxf(mx, __uint_as_float(acc[i]) * sc);
+          if (mx > -INFINITY) {
+            const float mn = fmaxf(*lse_m, mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c + i < c_end && vbase + i < p.V) sum += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
+            *lse_l = *lse_l * ex2_approx(*lse_m - mn) + sum;
+            *lse_m = mn;
+          }
+        }
+      }
       if (e.ret_logits && s == 0) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -323,7 +345,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 }
 
 // ---- the kernel ------------------------------------------------------------------
-template <int MT>
+template <int MT, bool LSE = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
                    const __grid_constant__ CUtensorMap h_map, const __grid_constant__ CUtensorMap w_map_t1,
@@ -529,6 +551,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
 
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
+    float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
 
     TileWalk walk(units_total, n_tiles, tail1, tail2);
     const int total_tiles = walk.count();
@@ -556,7 +579,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
+          scan_tile_columns<LSE>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi, &lse_m, &lse_l);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.B + b;
@@ -587,6 +610,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
         }
       }
+      if constexpr (LSE) lse_atomic_merge(&p.lse[b], lse_m, lse_l);
     }
   }
 
@@ -599,7 +623,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
+    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
   }
 }
 

@@ -141,6 +141,7 @@ struct PairWalk {
   }
 };
 
+template <bool LSE = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kUmmaThreads, 1)
 umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
                         const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int units_total,
@@ -307,6 +308,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
     float best_val = -INFINITY;
     int best_idx = kIdxNone;
+    float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
 
     PairWalk walk(units_total, n_tiles);
     for (int t = 0, ta = 0; t < n_tiles; ++t) {
@@ -332,7 +334,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
+          scan_tile_columns<LSE>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi, &lse_m, &lse_l);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.B + b;
@@ -362,6 +364,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
           if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
         }
       }
+      if constexpr (LSE) lse_atomic_merge(&p.lse[b], lse_m, lse_l);
     }
   }
 
@@ -375,7 +378,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
   }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
+    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
   }
 }
 

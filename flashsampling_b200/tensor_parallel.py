@@ -47,6 +47,45 @@ def reduce_gathered(vals: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor
     return win_id, best
 
 
+def combine_logprobs(
+    vals: torch.Tensor, ids: torch.Tensor, logprobs: torch.Tensor, lse: torch.Tensor
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Global winners and their log-probabilities from per-shard results.
+
+    ``vals``, ``ids``, ``logprobs`` are ``[world, B, S]``: every shard's winner, and its
+    log-probability under the shard's own normaliser ``lse`` ``[world, B]``.  The global
+    normaliser is the log-sum-exp of the shards' normalisers; the winning shard's
+    log-probability is shifted from its own normaliser to the global one.
+    """
+    world = vals.shape[0]
+    win_id, best = reduce_gathered(vals.reshape(world, -1), ids.reshape(world, -1))
+    win_id, best = win_id.view(vals.shape[1:]), best.view(vals.shape[1:])
+    owner = (ids == win_id.unsqueeze(0)) & (vals == best.unsqueeze(0))  # exactly one shard per item
+    shard_logit = logprobs + lse.unsqueeze(-1)  # logit / T of each shard's winner
+    win_logit = torch.where(owner, shard_logit, torch.zeros_like(shard_logit)).sum(dim=0)
+    lse_global = torch.logsumexp(lse.float(), dim=0)  # [B]
+    return win_id, best, win_logit - lse_global.unsqueeze(-1)
+
+
+def reduce_gathered_logprobs(exchange, ids, vals, logprobs, lse):
+    """all_gather of the shards' winners, log-probabilities and normalisers, then
+    ``combine_logprobs``; every rank ends with the same three tensors."""
+    world = exchange.tp.size
+    group = getattr(exchange, "group", None)
+    B, S = ids.shape
+    packed = torch.cat([vals.reshape(-1), logprobs.reshape(-1), lse.reshape(-1)]).contiguous()
+    g_packed = torch.empty(world * packed.numel(), dtype=packed.dtype, device=packed.device)
+    g_ids = torch.empty(world * ids.numel(), dtype=ids.dtype, device=ids.device)
+    dist.all_gather_into_tensor(g_packed, packed, group=group)
+    dist.all_gather_into_tensor(g_ids, ids.reshape(-1).contiguous(), group=group)
+    g_packed = g_packed.view(world, -1)
+    n = B * S
+    return combine_logprobs(
+        g_packed[:, :n].reshape(world, B, S), g_ids.view(world, B, S),
+        g_packed[:, n:2 * n].reshape(world, B, S), g_packed[:, 2 * n:].reshape(world, B),
+    )
+
+
 class CollectiveExchange:
     """all_gather through torch.distributed (NCCL baseline on GPUs, gloo on CPU)."""
 

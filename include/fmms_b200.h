@@ -49,6 +49,8 @@ extern "C" {
                                       replay once the caller advances the value between replays       */
 #define FMMS_FLAG_TWO_STAGE 32     /* decode the winners in a second kernel (the reference's
                                       stage 2, core.py:359-370) instead of the last CTA        */
+#define FMMS_FLAG_LOGPROB 128      /* set by fmms_sample_logprobs(): the pass also accumulates each
+                                      row's log-sum-exp and reports ln p(sampled id)            */
 
 /* kernel paths reported by fmms_last_path() */
 #define FMMS_PATH_NONE 0
@@ -156,6 +158,27 @@ int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperat
                    size_t workspace_bytes, int* status_dev, void* stream, int rank, int world,
                    int max_items, void* const* peer_buffers, unsigned int epoch,
                    unsigned long long wait_limit_ns);
+
+/* fmms_sample() that also reports, from the same pass over W, the log-probability of every
+ * sampled id under softmax(logits / T) and each row's log-normaliser:
+ *   out_logprob [B, S] fp32 (required)  ln p(out_idx[b, s]) = logit / T - out_lse[b]
+ *   out_lse     [B]    fp32 (nullable)  ln sum_v exp(logit_v / T) over this call's V_local rows
+ * Rows decoded greedily (FMMS_FLAG_GREEDY, or temperature <= 0) use T = 1.  The kernels keep a
+ * running (max, sum) per row next to the running argmax and merge the per-CTA partial sums with
+ * compare-and-swap; the winner's logit is its perturbed value minus its own noise, which is a
+ * pure function of (seed, draw, row, id).  The merge order is not fixed, so the two outputs are
+ * reproducible to fp32 rounding, not bit for bit; the sampled ids are unaffected.  Not combined
+ * with FMMS_FLAG_TWO_STAGE or with fmms_sample_tp() (FMMS_ERR_UNSUPPORTED): under tensor
+ * parallelism call this on the local shard and combine out_lse across ranks.
+ * The reference has no counterpart: it lists log-probabilities as unavailable without the full
+ * logits (findings/vllm-integration.md:99); the accumulation is the online log-sum-exp that its
+ * paper's appendix on optional outputs describes. */
+int fmms_sample_logprobs(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
+                         int V_local, int D, int B, int S, unsigned long long seed,
+                         long long v_global_offset, int flags, const float* ext_noise, long long noise_ld,
+                         float* logits_out, long long* out_idx, float* out_val, void* workspace,
+                         size_t workspace_bytes, int* status_dev, void* stream, float* out_logprob,
+                         float* out_lse);
 
 /* Size of one rank's symmetric buffer for `world` ranks and up to `max_items` (B * S)
  * items per step. */

@@ -259,6 +259,21 @@ def softmax_probs(logits_row: torch.Tensor, temperature: float) -> np.ndarray:
     return torch.softmax(z, dim=0).numpy()
 
 
+def log_probs(logits: torch.Tensor, temperature, ids: torch.Tensor):
+    """ln softmax(logits / T)[ids] and the log-normaliser, in fp64.
+
+    ``logits`` [B, V], ``temperature`` scalar or [B] (values <= 0 mean greedy
+    rows, which use T = 1), ``ids`` [B, S].  The same quantities as
+    core.py:57 + :95 of the reference (fp32 logits / T, softmax), taken in log
+    space.  Returns (log-probabilities [B, S], log-normaliser [B]).
+    """
+    t = torch.as_tensor(temperature, dtype=torch.float64).reshape(-1)
+    t = torch.where(t > 0, t, torch.ones_like(t))
+    z = logits.double() / (t[:, None] if t.numel() > 1 else t)
+    lse = torch.logsumexp(z, dim=-1)
+    return z.gather(1, ids.long()) - lse[:, None], lse
+
+
 def weight_read_time_us(vocab: int, hidden: int, tb_per_s: float = 8.0) -> float:
     """Pure weight-streaming time of a [vocab, hidden] bf16 matrix in microseconds."""
     return 2.0 * vocab * hidden / (tb_per_s * 1e12) * 1e6

@@ -1,0 +1,186 @@
+"""GPU parity of the log-probability output: ``return_logprobs`` / ``fmms_sample_logprobs``.
+
+The sampled ids must be the ones the plain call draws (bit for bit); the reported
+log-probabilities and log-normalisers are compared with the oracle's fp64
+``log_softmax(logits / T)`` of the fp32 logits.  Tolerance 1e-3 absolute: the kernel
+accumulates the sum in fp32 with ``ex2.approx`` and recovers the winner's logit as its
+perturbed value minus its noise.
+"""
+
+import pytest
+import torch
+
+from oracle import fmms_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def fs():
+    import flashsampling_b200 as fs
+    from flashsampling_b200 import build
+
+    build.build_library()
+    assert torch.cuda.is_available(), "GPU tests need a B200"
+    return fs
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _head(V, D, B, w_std=0.08, seed=0):
+    from flashsampling_b200.testing import gaussian_head
+
+    return gaussian_head(V, D, B, w_std, seed)
+
+
+def _check(ids, logprobs, logits_cpu, temps, label):
+    want, _ = O.log_probs(logits_cpu, temps, ids.cpu())
+    got = logprobs.cpu().double()
+    assert torch.isfinite(got).all(), label
+    err = (got - want).abs().max().item()
+    assert err < ATOL, f"{label}: log-probabilities off by {err:.3g}"
+
+
+# kernel, V, D, B, S: the weight-streaming kernel at every row-group shape, the tensor-core kernel
+# with one and two M tiles, ragged vocabularies, several K slabs, and the CTA-pair kernel
+CASES = [
+    ("gemv", 5000, 264, 1, 1),
+    ("gemv", 4097, 512, 2, 3),
+    ("gemv", 3000, 72, 5, 2),
+    ("gemv", 2048, 256, 8, 4),
+    ("mma", 129, 72, 3, 1),
+    ("mma", 9000, 264, 17, 2),
+    ("mma", 40000, 512, 64, 1),
+    ("mma", 20000, 256, 128, 3),
+    ("mma", 7000, 136, 200, 1),
+    ("mma", 33000, 128, 256, 2),  # CTA pairs (B > 128, V >= 32768, D % 64 == 0)
+]
+
+
+@pytest.mark.parametrize("kernel,V,D,B,S", CASES)
+def test_logprobs_match_log_softmax(fs, kernel, V, D, B, S):
+    w, h = _head(V, D, B, seed=V % 7)
+    wd, hd = w.to(_dev()), h.to(_dev())
+    g = torch.Generator().manual_seed(3)
+    temps = torch.rand(B, generator=g) * 1.2 + 0.4
+    if B > 2:
+        temps[1] = 0.0  # a greedy row inside the batch
+    td = temps.to(_dev())
+    logits = O.logits_fp32(w, h)
+
+    plain = fs.fused_mm_sample(wd, hd, S, td, seed=11, kernel=kernel)
+    ids, vals, lp = fs.fused_mm_sample(wd, hd, S, td, seed=11, kernel=kernel, return_values=True,
+                                       return_logprobs=True)
+    assert fs.last_path() == kernel
+    fs.check_status()
+    assert torch.equal(ids, plain), "the log-probability variant must draw the same ids"
+    assert lp.shape == (B, S) and lp.dtype == torch.float32
+    _check(ids, lp, logits, temps, f"{kernel} V={V} B={B} S={S}")
+    assert (lp <= 1e-4).all()
+
+    # the log-sum-exp slots are left clean: a second call (other seed) is as accurate, and a
+    # plain call afterwards still draws the plain ids
+    ids2, lp2 = fs.fused_mm_sample(wd, hd, S, td, seed=12, kernel=kernel, return_logprobs=True)
+    _check(ids2, lp2, logits, temps, f"{kernel} V={V} B={B} S={S} (second call)")
+    assert torch.equal(fs.fused_mm_sample(wd, hd, S, td, seed=11, kernel=kernel), plain)
+    fs.check_status()
+
+
+@pytest.mark.parametrize("kernel,B", [("gemv", 2), ("mma", 40)])
+def test_logprobs_with_external_noise_and_greedy(fs, kernel, B):
+    V, D, S = 6000, 256, 2
+    w, h = _head(V, D, B, seed=2)
+    wd, hd = w.to(_dev()), h.to(_dev())
+    logits = O.logits_fp32(w, h)
+    g = torch.Generator().manual_seed(8)
+    noise = O.gumbel_from_uniform(torch.rand(S, B, V, generator=g).clamp_min(1e-30))
+    t = torch.tensor(0.75, device=_dev())
+    ids, lp = fs.fused_mm_sample(wd, hd, S, t, seed=0, noise=noise.to(_dev()), kernel=kernel, return_logprobs=True)
+    want, decisive, _ = O.gumbel_argmax(logits, 0.75, noise, rel_gap=1e-3)
+    assert not ((ids.cpu() != want) & decisive).any()
+    _check(ids, lp, logits, 0.75, f"{kernel} external noise")
+
+    ids, lp = fs.fused_mm_sample(wd, hd, 1, t, seed=0, greedy_sampling=True, kernel=kernel, return_logprobs=True)
+    _check(ids, lp, logits, 1.0, f"{kernel} greedy")  # greedy decoding reports T = 1 probabilities
+    top2 = logits.topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 1e-3
+    assert torch.equal(ids.cpu()[clear, 0], logits.argmax(-1)[clear])
+    fs.check_status()
+
+
+def test_logprobs_over_batches_above_one_launch(fs):
+    """More than 256 rows run as consecutive launches; every block reports its own rows."""
+    V, D, B = 3000, 136, 300
+    w, h = _head(V, D, B, seed=6)
+    t = torch.tensor(0.9, device=_dev())
+    ids, lp = fs.fused_mm_sample(w.to(_dev()), h.to(_dev()), 1, t, seed=4, return_logprobs=True)
+    fs.check_status()
+    assert torch.equal(ids, fs.fused_mm_sample(w.to(_dev()), h.to(_dev()), 1, t, seed=4))
+    _check(ids, lp, O.logits_fp32(w, h), 0.9, "B=300")
+
+
+def test_c_abi_reports_the_log_normaliser_and_rejects_unsupported_modes(fs):
+    from flashsampling_b200 import _lib
+
+    lib = _lib.load()
+    V, D, B, S = 4096, 128, 6, 2
+    w, h = _head(V, D, B, seed=1)
+    wd, hd = w.to(_dev()), h.to(_dev())
+    t = torch.tensor([0.8], device=_dev())
+    out = torch.empty((B, S), dtype=torch.int64, device=_dev())
+    lp = torch.empty((B, S), dtype=torch.float32, device=_dev())
+    lse = torch.empty((B,), dtype=torch.float32, device=_dev())
+    wsz = _lib.query_workspace(V, D, B, S)
+    ws = torch.zeros(wsz, dtype=torch.uint8, device=_dev())
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (wd.data_ptr(), hd.data_ptr(), t.data_ptr(), 0, V, D, B, S, 5, 0)
+    tail = (None, 0, None, out.data_ptr(), None, ws.data_ptr(), wsz, None, stream)
+    assert lib.fmms_sample_logprobs(*args, 0, *tail, lp.data_ptr(), lse.data_ptr()) == _lib.OK
+    torch.cuda.synchronize()
+    want_lp, want_lse = O.log_probs(O.logits_fp32(w, h), 0.8, out.cpu())
+    assert (lp.cpu().double() - want_lp).abs().max() < ATOL
+    assert (lse.cpu().double() - want_lse).abs().max() < ATOL
+    head = 256 + 256 * 8 + B * S * 8  # counter, log-sum-exp slots and keys are zero again
+    assert int(ws[:head].count_nonzero()) == 0
+    # the log-probability output is required; the two-stage mode does not carry it
+    assert lib.fmms_sample_logprobs(*args, 0, *tail, None, None) == _lib.ERR_BAD_ARG
+    assert lib.fmms_sample_logprobs(*args, _lib.FLAG_TWO_STAGE, *tail, lp.data_ptr(), None) == _lib.ERR_UNSUPPORTED
+
+
+def test_shard_results_combine_to_the_unsharded_log_probabilities(fs):
+    """Vocabulary blocks sampled one after another on one GPU with their global offsets, then
+    combined the way tensor-parallel ranks combine them after the all-gather."""
+    from flashsampling_b200 import _lib
+    from flashsampling_b200.tensor_parallel import combine_logprobs
+
+    lib = _lib.load()
+    V, D, B, S = 8192, 256, 20, 2
+    w, h = _head(V, D, B, seed=13)
+    hd = h.to(_dev())
+    t = torch.tensor([1.1], device=_dev())
+    stream = torch.cuda.current_stream().cuda_stream
+    wsz = _lib.query_workspace(V, D, B, S)
+    ws = torch.zeros(wsz, dtype=torch.uint8, device=_dev())
+    parts = []
+    for lo, hi in ((0, 2048), (2048, 4096), (4096, 6144), (6144, 8192)):
+        wd = w[lo:hi].contiguous().to(_dev())
+        out = torch.empty((B, S), dtype=torch.int64, device=_dev())
+        val = torch.empty((B, S), dtype=torch.float32, device=_dev())
+        lp = torch.empty((B, S), dtype=torch.float32, device=_dev())
+        lse = torch.empty((B,), dtype=torch.float32, device=_dev())
+        rc = lib.fmms_sample_logprobs(
+            wd.data_ptr(), hd.data_ptr(), t.data_ptr(), 0, hi - lo, D, B, S, 21, lo, 0, None, 0, None,
+            out.data_ptr(), val.data_ptr(), ws.data_ptr(), wsz, None, stream, lp.data_ptr(), lse.data_ptr(),
+        )
+        assert rc == _lib.OK
+        torch.cuda.synchronize()
+        parts.append((val, out, lp, lse))
+    ids, vals, lp = combine_logprobs(*(torch.stack(x) for x in zip(*parts)))
+    whole_ids, whole_lp = fs.fused_mm_sample(w.to(_dev()), hd, S, t[0], seed=21, return_logprobs=True)
+    assert torch.equal(ids, whole_ids)
+    assert (lp - whole_lp).abs().max() < ATOL
+    _check(ids, lp, O.logits_fp32(w, h), 1.1, "combined shards")

@@ -43,6 +43,38 @@ def test_vocab_sharded_draw_equals_unsharded_draw_gloo(world):
     run_maybe_distributed(_tp_worker, world, world, 17)
 
 
+def _tp_logprob_worker(world, seed):
+    """Every rank reports its block's winner, that winner's log-probability under the block's own
+    normaliser, and the normaliser; after the all-gather all ranks hold the unsharded values."""
+    from flashsampling_b200.tensor_parallel import CollectiveExchange, reduce_gathered_logprobs
+    from flashsampling_b200.testing import gaussian_head, shard_weights
+    from flashsampling_b200.tp_info import TPInfo
+    from oracle import fmms_oracle as O
+
+    tp = TPInfo.from_world()
+    V, D, B, S, T = 1024, 64, 5, 3, 0.9
+    w, h = gaussian_head(V, D, B, 0.2, seed=seed)
+    noise = O.kernel_noise(seed, S, B, 0, V)
+    logits = O.logits_fp32(w, h)
+    full_idx, _, _ = O.gumbel_argmax(logits, T, noise)
+    full_lp, _ = O.log_probs(logits, T, full_idx)
+    lo, hi = tp.shard_rows(V)
+    loc_logits = O.logits_fp32(shard_weights(w, tp), h)
+    loc_idx, _, loc_val = O.gumbel_argmax(loc_logits, T, noise[:, :, lo:hi])
+    loc_lp, loc_lse = O.log_probs(loc_logits, T, loc_idx)
+    ex = CollectiveExchange(tp, torch.device("cpu"))
+    ids, vals, lp = reduce_gathered_logprobs(ex, loc_idx + lo, loc_val, loc_lp.float(), loc_lse.float())
+    assert torch.equal(ids, full_idx)
+    assert (lp.double() - full_lp).abs().max() < 1e-5, (tp.rank, lp, full_lp)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_log_probabilities_renormalise_gloo(world):
+    from flashsampling_b200.tp_info import run_maybe_distributed
+
+    run_maybe_distributed(_tp_logprob_worker, world, world, 23)
+
+
 def test_shard_rows_cover_vocab_without_overlap():
     from flashsampling_b200.tp_info import TPInfo
 
