@@ -127,13 +127,17 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, int b
 }
 
 // Workspace layout, a function of the workspace SIZE only (so calls of different shapes that
-// share one workspace agree on it): [ticket: 256 B][log-sum-exp slots: 256 u64][keys: cap u64]
-// [running candidates: kMaxParts * cap * (f32 + i32)], cap = the number of (row, draw) items the
-// size can hold.  Ticket, slots and keys must be zero when a call starts; every call leaves them
-// zero again.
+// share one workspace agree on it): [ticket: 256 B][log-sum-exp scratch: kLseMaxSplit x 256 u64 of
+// the last CTA's merge, then kMaxLseParts x 256 u64 per-CTA partial sums][keys: cap u64][running candidates:
+// kMaxParts * cap * (f32 + i32)], cap = the number of (row, draw) items the size can hold.
+// Ticket and keys must be zero when a call starts; every call leaves them zero again.  The
+// log-sum-exp scratch needs no initial state: a launch writes every entry it later reads.
 constexpr int kMaxBatchPerLaunch = 256;
-constexpr size_t kWsLseOffset = 256;
-constexpr size_t kWsHeadBytes = kWsLseOffset + (size_t)kMaxBatchPerLaunch * 8;
+constexpr int kMaxLseParts = kMaxParts / 4;  // one partial row per CTA (or CTA pair)
+static_assert(kMaxBatchPerLaunch == kLseMaxRows, "the log-sum-exp scratch is sized for one launch's rows");
+constexpr size_t kWsLse2Offset = 256;
+constexpr size_t kWsLseOffset = kWsLse2Offset + (size_t)kLseMaxSplit * kLseMaxRows * 8;
+constexpr size_t kWsHeadBytes = kWsLseOffset + (size_t)kMaxLseParts * kMaxBatchPerLaunch * 8;
 static size_t workspace_bytes_for(int B, int S) {
   return kWsHeadBytes + (size_t)B * (size_t)S * 8 * (1 + (size_t)kMaxParts);
 }
@@ -265,6 +269,8 @@ static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream
   const size_t smem = gemv_smem_bytes(NB, p.D, p.stages, p.gemv_chunks);
   const int groups = (p.V + kGemvRows - 1) / kGemvRows;
   const int grid = groups < d.num_sms ? groups : d.num_sms;
+  if ((p.flags & kFlagLogprob) && grid > kMaxLseParts) return -kErrUnsupported;
+  p.lse_parts = grid;
   switch (NB) {
     case 1: rc = launch_gemv_nb<1>(d, map, p, grid, smem, stream); break;
     case 2: rc = launch_gemv_nb<2>(d, map, p, grid, smem, stream); break;
@@ -369,6 +375,7 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * 16;
   p.tiles_per_cta = pl.tiles_per_cta;
+  p.lse_parts = pl.grid;
   rc = pl.mt == 1 ? launch_umma_mt<1>(d, mp, p, pl, stream) : launch_umma_mt<2>(d, mp, p, pl, stream);
   if (rc != kOk) return -rc;
   return pl.grid * kUmmaEpiGroups;
@@ -411,6 +418,7 @@ static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleP
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * kPairUnitRows;
   p.tiles_per_cta = pl.tiles_per_pair;
+  p.lse_parts = pl.grid / 2;
   if (lse)
     umma_pair_sample_kernel<true><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total,
                                                                               pl.q_units, pl.slabs);
@@ -650,6 +658,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
   p.ticket = reinterpret_cast<unsigned int*>(ws);
   p.sched = p.ticket + 1;
   p.lse = reinterpret_cast<unsigned long long*>(ws + kWsLseOffset);
+  p.lse2 = reinterpret_cast<unsigned long long*>(ws + kWsLse2Offset);
   p.out_logprob = out_logprob;
   p.out_lse = out_lse;
   p.keys = reinterpret_cast<unsigned long long*>(ws + kWsHeadBytes);

@@ -155,26 +155,16 @@ __device__ __forceinline__ void lse_push(float& m, float& l, float x2) {
   m = mn;
 }
 
-// Merge a partial sum into the row's 64-bit slot (m in the high word, l in the low word; zero =
-// empty) with a compare-and-swap loop: every failed attempt means another partial got in.
-__device__ __forceinline__ void lse_atomic_merge(unsigned long long* slot, float m, float l) {
-  if (!(l > 0.f)) return;
-  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(slot);
-  for (int tries = 0; tries < (1 << 20); ++tries) {  // at most one retry per competing partial
-    float mn = __uint_as_float((uint32_t)(old >> 32)), ln = __uint_as_float((uint32_t)old);
-    lse_merge(mn, ln, m, l);
-    const unsigned long long neu = ((unsigned long long)__float_as_uint(mn) << 32) | __float_as_uint(ln);
-    const unsigned long long prev = atomicCAS(slot, old, neu);
-    if (prev == old) break;
-    old = prev;
-  }
+// A partial sum as one 64-bit word (m in the high half, l in the low half; zero = empty).
+__device__ __forceinline__ unsigned long long lse_pack(float m, float l) {
+  return ((unsigned long long)__float_as_uint(m) << 32) | __float_as_uint(l);
+}
+__device__ __forceinline__ void lse_merge_packed(float& m, float& l, unsigned long long bits) {
+  lse_merge(m, l, __uint_as_float((uint32_t)(bits >> 32)), __uint_as_float((uint32_t)bits));
 }
 
-// Natural-log normaliser ln(sum_v exp(logit_v / T)) from a slot's bits.
-__device__ __forceinline__ float lse_value(unsigned long long bits) {
-  const float m = __uint_as_float((uint32_t)(bits >> 32)), l = __uint_as_float((uint32_t)bits);
-  return (m + log2f(l)) * kLn2f;
-}
+// Natural-log normaliser ln(sum_v exp(logit_v / T)).
+__device__ __forceinline__ float lse_value(float m, float l) { return (m + log2f(l)) * kLn2f; }
 
 // ------------------------------------------------------------------------------------
 // PTX wrappers

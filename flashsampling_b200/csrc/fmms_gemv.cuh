@@ -33,6 +33,9 @@ constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;       // + producer 
 constexpr int kGemvMaxBatch = 8;
 constexpr int kGemvMaxStages = 6;  // ring depth cap: ~96-128 KiB in flight per SM, deeper rings measured slower
 
+constexpr int kLseMaxSplit = 16;  // partial sums per row left by the first merge step
+constexpr int kLseMaxRows = 256;  // batch rows per launch
+
 struct SampleParams {
   const __nv_bfloat16* H;    // [B, D]
   const float* temperature;  // [1] or [B]
@@ -53,8 +56,10 @@ struct SampleParams {
   int* cand_idx;
   long long* out_idx;        // [B, S]
   float* out_val;            // [B, S] or null
-  // kFlagLogprob: per-row log-sum-exp slots (zero on entry and on exit) and the outputs
-  unsigned long long* lse;   // [B] packed (m, l)
+  // kFlagLogprob: per-CTA partial log-sum-exps, the rows' normalisers, and the outputs
+  unsigned long long* lse;   // [lse_parts, B] packed (m, l); every launch writes all it reads
+  unsigned long long* lse2;  // [kLseMaxSplit, kLseMaxRows] scratch of the last CTA's two-step merge
+  int lse_parts;             // CTAs (CTA pairs) that write a partial row
   float* out_logprob;        // [B, S] ln p(sampled id)
   float* out_lse;            // [B] ln sum_v exp(logit_v / T), or null
   int* status_dev;
@@ -108,6 +113,48 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   if (!*is_last) return;
   __threadfence();
   const int n = p.B * p.S;
+  // kFlagLogprob, first step: the CTAs' partial sums [lse_parts][B] shrink to [lse_k][B].  A warp
+  // takes up to 32 consecutive rows (coalesced loads; with fewer rows the spare lanes share the
+  // partial rows and a shuffle tree joins them) and every lse_k-th share of the partial rows.  The
+  // merge order is fixed, so the result is reproducible bit for bit.
+  int lse_k = 1;
+  if constexpr (LSE) {
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+    const int nblk = (p.B + 31) >> 5;  // <= 8 <= nwarps
+    lse_k = min(nwarps / nblk, kLseMaxSplit);
+    int rows = 32;  // rows per warp: 32, or the batch rounded up to a power of two
+    if (p.B < 32) {
+      rows = 1;
+      while (rows < p.B) rows <<= 1;
+    }
+    if (warp < nblk * lse_k) {  // warp-uniform
+      const int per_row = 32 / rows;  // lanes that share a row
+      const int b = (warp % nblk) * 32 + (lane & (rows - 1)), j = warp / nblk;
+      const int step = lse_k * per_row;
+      float m = -INFINITY, l = 0.f;
+      if (b < p.B) {
+        int part = j * per_row + lane / rows;
+        for (; part + 3 * step < p.lse_parts; part += 4 * step) {  // four loads in flight
+          unsigned long long x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            x[u] = *reinterpret_cast<volatile unsigned long long*>(&p.lse[(size_t)(part + u * step) * p.B + b]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) lse_merge_packed(m, l, x[u]);
+        }
+        for (; part < p.lse_parts; part += step)
+          lse_merge_packed(m, l, *reinterpret_cast<volatile unsigned long long*>(&p.lse[(size_t)part * p.B + b]));
+      }
+      for (int off = rows; off < 32; off <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+        lse_merge(m, l, m2, l2);
+      }
+      if (lane < rows && b < p.B) p.lse2[(size_t)j * kLseMaxRows + b] = lse_pack(m, l);
+    }
+    __threadfence_block();
+    sync();
+  }
   if (p.tp_world <= 1) {
     for (int item = tid; item < n; item += nthreads) {
       const unsigned long long k = atomicExch(&p.keys[item], 0ull);
@@ -118,14 +165,14 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
       p.out_idx[(size_t)b * p.S + s] = p.v_offset + idx;
       if (p.out_val) p.out_val[(size_t)b * p.S + s] = v;
       if constexpr (LSE) {
-        const float lse = lse_value(*reinterpret_cast<volatile unsigned long long*>(&p.lse[b]));
+        // second step: the row's lse_k partial sums, then the winner's log-probability
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < lse_k; ++j)
+          lse_merge_packed(m, l, *reinterpret_cast<volatile unsigned long long*>(&p.lse2[(size_t)j * kLseMaxRows + b]));
+        const float lse = lse_value(m, l);
         p.out_logprob[(size_t)b * p.S + s] = winner_logprob(p, b, s, v, idx, lse);
         if (s == 0 && p.out_lse) p.out_lse[b] = lse;
       }
-    }
-    if constexpr (LSE) {
-      sync();  // every draw of a row has read the row's slot
-      for (int b = tid; b < p.B; b += nthreads) p.lse[b] = 0ull;
     }
     if (tid == 0) {
       *p.ticket = 0u;
@@ -494,7 +541,7 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
       float m = red_val[tid], l = red_l[tid];
 #pragma unroll
       for (int w = 1; w < kGemvConsumerWarps; ++w) lse_merge(m, l, red_val[w * 32 + tid], red_l[w * 32 + tid]);
-      lse_atomic_merge(&p.lse[tid], m, l);
+      p.lse[(size_t)blockIdx.x * p.B + tid] = lse_pack(m, l);  // this CTA's partial row
     }
   }
   if (!(p.flags & kFlagTwoStage)) {

@@ -253,38 +253,46 @@ struct EpiRow {
   unsigned long long seed;
 };
 
+// kFlagLogprob: fold the scaled logits of columns [c_begin, c_end) of the accumulator tile into
+// the thread's running log-sum-exp - one maximum and one rescale per 32-column chunk.  A pass of
+// its own over the tile (TMEM reads are cheap), so that the sampling scan keeps its registers.
+__device__ __forceinline__ void lse_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
+                                                 int c_begin, int c_end, int v0, float& lse_m, float& lse_l) {
+  const float sc = e.inv_t * kLog2e;  // > 0: the largest logit gives the largest scaled logit
+  for (int c = c_begin; c < c_end; c += 32) {
+    uint32_t acc[32];
+    tmem_ld32(t_addr + (uint32_t)c, acc);
+    if (e.row_ok) {
+      const int n_ok = min(c_end - c, p.V - (v0 + c));  // valid columns of this chunk
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < n_ok) mx = fmaxf(mx, __uint_as_float(acc[i]));
+      if (mx > -INFINITY) {
+        const float mn = fmaxf(lse_m, mx * sc);
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          if (i < n_ok) sum0 += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
+          if (i + 1 < n_ok) sum1 += ex2_approx(fmaf(__uint_as_float(acc[i + 1]), sc, -mn));
+        }
+        lse_l = lse_l * ex2_approx(lse_m - mn) + (sum0 + sum1);
+        lse_m = mn;
+      }
+    }
+  }
+}
+
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
 // quadrant, first column of the tile) for draw `s`: scale, add noise, keep the running (max, id)
 // of the thread's row.  The tile's first column is vocabulary row v0 of this shard.
-// With LSE, draw 0 also folds the scaled logits of the columns into the thread's running
-// log-sum-exp (lse_m, lse_l): one maximum and one rescale per 32-column chunk.
-template <bool LSE = false>
 __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
-                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi,
-                                                  float* lse_m = nullptr, float* lse_l = nullptr) {
+                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
   for (int c = c_begin; c < c_end; c += 32) {
     uint32_t acc[32];
     tmem_ld32(t_addr + (uint32_t)c, acc);
     if (e.row_ok) {
       const int vbase = v0 + c;
-      if constexpr (LSE) {
-        if (s == 0) {
-          const float sc = e.inv_t * kLog2e;
-          float mx = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c + i < c_end && vbase + i < p.V) mx = fmaxf(mx, __uint_as_float(acc[i]) * sc);
-          if (mx > -INFINITY) {
-            const float mn = fmaxf(*lse_m, mx);
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c + i < c_end && vbase + i < p.V) sum += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
-            *lse_l = *lse_l * ex2_approx(*lse_m - mn) + sum;
-            *lse_m = mn;
-          }
-        }
-      }
       if (e.ret_logits && s == 0) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -572,6 +580,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       if (ew == 0 && lane == 0 && t == total_tiles - 1) stamp(p, 4);
       if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
+        if constexpr (LSE) lse_tile_columns(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
         for (int s = 0; s < S; ++s) {
           float bv = best_val;
           int bi = best_idx;
@@ -579,7 +588,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          scan_tile_columns<LSE>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi, &lse_m, &lse_l);
+          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.B + b;
@@ -610,7 +619,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
         }
       }
-      if constexpr (LSE) lse_atomic_merge(&p.lse[b], lse_m, lse_l);
+      // every tile has been multiplied, so the pipeline's first stage is free: it collects the
+      // column groups' partial sums of each row
+      if constexpr (LSE)
+        reinterpret_cast<unsigned long long*>(smem)[col_group * (MT * 128) + b] = lse_pack(lse_m, lse_l);
     }
   }
 
@@ -621,9 +633,20 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if constexpr (LSE) {
+    // one partial row per CTA: the column groups' sums merged in a fixed order
+    constexpr int kGroups = (MT == 2) ? kUmmaEpiGroups / 2 : kUmmaEpiGroups;
+    const unsigned long long* part = reinterpret_cast<const unsigned long long*>(smem);
+    for (int r = tid; r < MT * 128 && r < p.B; r += kUmmaThreads) {
+      float m = -INFINITY, l = 0.f;
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) lse_merge_packed(m, l, part[g * (MT * 128) + r]);
+      p.lse[(size_t)cta * p.B + r] = lse_pack(m, l);
+    }
+  }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
+    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/!LSE);
   }
 }
 

@@ -327,6 +327,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
       if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
       if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(j * nt_cap);
+        if constexpr (LSE) lse_tile_columns(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
         for (int s = 0; s < S; ++s) {
           float bv = best_val;
           int bi = best_idx;
@@ -334,7 +335,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          scan_tile_columns<LSE>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi, &lse_m, &lse_l);
+          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.B + b;
@@ -364,7 +365,10 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
           if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
         }
       }
-      if constexpr (LSE) lse_atomic_merge(&p.lse[b], lse_m, lse_l);
+      // every tile has been multiplied, so the pipeline's first stage is free: it collects the
+      // warpgroups' partial sums of this CTA's 128 rows
+      if constexpr (LSE)
+        reinterpret_cast<unsigned long long*>(smem)[wg * 128 + quad * 32 + lane] = lse_pack(lse_m, lse_l);
     }
   }
 
@@ -376,9 +380,21 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if constexpr (LSE) {
+    // one partial row per CTA pair: each CTA fills in its own 128 batch rows
+    const unsigned long long* part = reinterpret_cast<const unsigned long long*>(smem);
+    for (int r = tid; r < 128; r += kUmmaThreads) {
+      const int b = (int)rank * 128 + r;
+      if (b >= p.B) continue;
+      float m = -INFINITY, l = 0.f;
+#pragma unroll
+      for (int g = 0; g < kUmmaEpiGroups; ++g) lse_merge_packed(m, l, part[g * 128 + r]);
+      p.lse[(size_t)(cta >> 1) * p.B + b] = lse_pack(m, l);
+    }
+  }
   if (!(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
-    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/true);
+    finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/!LSE);
   }
 }
 

@@ -144,8 +144,8 @@ def test_c_abi_reports_the_log_normaliser_and_rejects_unsupported_modes(fs):
     want_lp, want_lse = O.log_probs(O.logits_fp32(w, h), 0.8, out.cpu())
     assert (lp.cpu().double() - want_lp).abs().max() < ATOL
     assert (lse.cpu().double() - want_lse).abs().max() < ATOL
-    head = 256 + 256 * 8 + B * S * 8  # counter, log-sum-exp slots and keys are zero again
-    assert int(ws[:head].count_nonzero()) == 0
+    keys_at = wsz - B * S * 8 * 641  # the head (CTA counter, log-sum-exp scratch) precedes the packed winners
+    assert int(ws[:256].count_nonzero()) == 0 and int(ws[keys_at:keys_at + B * S * 8].count_nonzero()) == 0
     # the log-probability output is required; the two-stage mode does not carry it
     assert lib.fmms_sample_logprobs(*args, 0, *tail, None, None) == _lib.ERR_BAD_ARG
     assert lib.fmms_sample_logprobs(*args, _lib.FLAG_TWO_STAGE, *tail, lp.data_ptr(), None) == _lib.ERR_UNSUPPORTED
