@@ -214,7 +214,7 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
  * allocates its candidate buffers with torch.empty on every call.
  *
  * Same arguments and results as fmms_sample() minus `workspace`: the candidate scratch
- * is an array built into the library's device image (about 5 MiB, resident on every
+ * is an array built into the library's device image (about 5.4 MiB, resident on every
  * GPU that loads the library until the process exits).  The call itself allocates
  * nothing, on the device or through any library.
  *
