@@ -116,7 +116,7 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   // kFlagLogprob, first step: the CTAs' partial sums [lse_parts][B] shrink to [lse_k][B].  A warp
   // takes up to 32 consecutive rows (coalesced loads; with fewer rows the spare lanes share the
   // partial rows and a shuffle tree joins them) and every lse_k-th share of the partial rows.  The
-  // merge order is fixed, so the result is reproducible bit for bit.
+  // merge order is fixed: with statically tiled kernels the result is reproducible bit for bit.
   int lse_k = 1;
   if constexpr (LSE) {
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;

@@ -24,10 +24,17 @@ class SamplingMetadata:
 
     temperature: torch.Tensor  # [num_requests] fp32 on the device; 0 = greedy for that request
     all_greedy: bool = False  # every request greedy: skip temperature and noise altogether
+    logprobs: bool = False  # also report ln p(sampled token) per request (the engine's `logprobs` field)
 
 
 class FMMSSampler:
-    """``sampler(lm_head_weight, hidden_states, metadata) -> int32 [num_requests]`` token ids."""
+    """``sampler(lm_head_weight, hidden_states, metadata) -> int32 [num_requests]`` token ids.
+
+    With ``metadata.logprobs`` the call returns ``(token ids, fp32 [num_requests] log-probabilities)``:
+    the engine's ``SamplerOutput(sampled_token_ids, logprobs)`` pair
+    (findings/vllm-integration.md:220), which the reference's hook leaves as ``None`` because it
+    has no logits to compute it from (:99, :325).
+    """
 
     def __init__(self, seed: int = 0, tp: TPInfo = TP1, device_seed: bool = False):
         """``device_seed=True`` keeps the step's seed in a device tensor that is advanced by a tiny
@@ -49,7 +56,7 @@ class FMMSSampler:
             seed = self._seed_t
         else:
             seed = self.seed + self.step  # draw s of a call uses stream seed + s: one fresh stream per step
-        ids = fused_mm_sample(
+        out = fused_mm_sample(
             weights=lm_head_weight,
             hidden_states=hidden_states,
             num_samples=1,
@@ -57,5 +64,9 @@ class FMMSSampler:
             seed=seed,
             greedy_sampling=sampling_metadata.all_greedy,
             tp=self.tp,
+            return_logprobs=sampling_metadata.logprobs,
         )
-        return ids[:, 0].to(torch.int32)
+        if sampling_metadata.logprobs:
+            ids, logprobs = out
+            return ids[:, 0].to(torch.int32), logprobs[:, 0]
+        return out[:, 0].to(torch.int32)

@@ -165,8 +165,9 @@ int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperat
  *   out_lse     [B]    fp32 (nullable)  ln sum_v exp(logit_v / T) over this call's V_local rows
  * Rows decoded greedily (FMMS_FLAG_GREEDY, or temperature <= 0) use T = 1.  The kernels keep a
  * running (max, sum) per row next to the running argmax; every CTA leaves one partial sum per
- * row in the workspace and the CTA that finishes last merges them in CTA order (reproducible
- * bit for bit); the winner's logit is its perturbed value minus its own noise, which is a
+ * row in the workspace and the CTA that finishes last merges them in a fixed order (bit for bit
+ * reproducible with the tensor-core kernels; to fp32 rounding with the weight-streaming kernel,
+ * whose CTAs share part of the work dynamically); the winner's logit is its perturbed value minus its own noise, which is a
  * pure function of (seed, draw, row, id).  The sampled ids are those of fmms_sample().  Not combined
  * with FMMS_FLAG_TWO_STAGE or with fmms_sample_tp() (FMMS_ERR_UNSUPPORTED): under tensor
  * parallelism call this on the local shard and combine out_lse across ranks.
