@@ -58,6 +58,16 @@ def _tp_worker(world):
     got = fs.fused_mm_sample(w_local, hd, S, t, seed=5, tp=tp, kernel="mma")  # eager again, same counter
     assert torch.equal(got, full)
     fs.check_status()
+    # log-probabilities: every rank reports on its block, the results are renormalised after an all-gather
+    V, D, B, S = 16384 - 16384 % world, 256, 48, 2
+    w, h = gaussian_head(V, D, B, 0.08, seed=11)
+    hd = h.to(dev)
+    full_ids, full_lp = fs.fused_mm_sample(w.to(dev), hd, S, t, seed=7, return_logprobs=True)
+    ids, lp = fs.fused_mm_sample(shard_weights(w, tp).contiguous().to(dev), hd, S, t, seed=7, tp=tp,
+                                 return_logprobs=True)
+    assert torch.equal(ids, full_ids), (tp.rank, (ids != full_ids).sum().item())
+    assert float((lp - full_lp).abs().max()) < 1e-3
+    fs.check_status()
     # the reference's distributed protocol: chi-square per rank on sharded ramps (testing.py:264-275)
     for V, nh in ((256, 2), (512, 1)):
         assert_sampling_distribution("fused-triton", V, nh, tp=tp)
