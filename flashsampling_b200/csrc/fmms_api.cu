@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -27,7 +28,7 @@ static thread_local int g_last_path = FMMS_PATH_NONE;
 static unsigned long long* g_stamps = nullptr;  // see fmms_debug_stamps()
 
 struct DeviceInfo {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   int num_sms = 0;
   int cc_major = 0;
   int max_smem_optin = 0;
@@ -43,13 +44,13 @@ static int device_info(DeviceInfo** out) {
   if (cudaGetDevice(&dev) != cudaSuccess) return kErrCuda;
   if (dev < 0 || dev >= kMaxDevices) return kErrUnsupported;
   DeviceInfo& d = g_dev[dev];
-  if (!d.ready) {
+  if (!d.ready.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_relaxed)) {
       if (cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return kErrCuda;
       if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return kErrCuda;
       if (cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return kErrCuda;
-      d.ready = true;
+      d.ready.store(true, std::memory_order_release);
     }
   }
   *out = &d;
@@ -62,20 +63,17 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                    CUtensorMapFloatOOBfill);
 
+static EncodeTiledFn lookup_encode_fn() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    return reinterpret_cast<EncodeTiledFn>(p);
+  return nullptr;
+}
+
 static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (!tried) {
-      void* p = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-          q == cudaDriverEntryPointSuccess)
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-      tried = true;
-    }
-  }
+  static const EncodeTiledFn fn = lookup_encode_fn();  // initialised once, thread-safe
   return fn;
 }
 
@@ -761,7 +759,10 @@ int fmms_tp_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_64) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
   void* p = nullptr;
   if (cudaMalloc(&p, bytes) != cudaSuccess) return FMMS_ERR_CUDA;
-  if (cudaMemset(p, 0, bytes) != cudaSuccess) return FMMS_ERR_CUDA;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess) {
+    cudaFree(p);
+    return FMMS_ERR_CUDA;
+  }
   cudaIpcMemHandle_t h;
   if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
     cudaFree(p);
