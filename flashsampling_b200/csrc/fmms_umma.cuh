@@ -8,13 +8,14 @@
 // batch row and walks vocabulary columns in order: the Gumbel-max scan is a running
 // (max, index) in two registers, with no cross-lane traffic until the kernel ends.
 //
-// Warp roles (384 threads, one CTA per SM, persistent over a contiguous range of
+// Warp roles (640 threads, one CTA per SM, persistent over a contiguous range of
 // vocabulary tiles):
 //   warp 0, 2   TMA producers: W tile / hidden-state tile(s) of each pipeline stage
 //   warp 1      TMEM allocation, then one elected thread issues tcgen05.mma/commit
-//   warps 4-11  epilogue: tcgen05.ld -> scale, noise, running argmax.  TMEM
-//               accumulators are multi-buffered so the epilogue of tile i overlaps
-//               the mainloop of tile i+1.
+//   warp 3      idle
+//   warps 4-19  epilogue (four warpgroups that split a tile's columns): tcgen05.ld ->
+//               scale, noise, running argmax.  TMEM accumulators are multi-buffered
+//               so the epilogue of tile i overlaps the mainloop of tile i+1.
 // Batches above 128 use two M tiles that share every W tile (MT = 2).
 #pragma once
 

@@ -38,6 +38,16 @@ def test_workspace_query_and_bad_arguments(lib):
     assert rc == _lib.ERR_BAD_ARG
     rc = lib.fmms_sample_static(None, None, None, 0, 10, 8, 64, 64, 0, 0, 0, None, 0, None, None, None, None, None)
     assert rc == _lib.ERR_TOO_LARGE
+    # the log-probability entry point: same checks, plus its required output and the modes it excludes
+    fake = ctypes.c_void_p(4096)  # never dereferenced: the checks below fail before any CUDA call
+    base = (fake, fake, fake, 0, 10, 8, 1, 1, 0, 0)
+    rest = (None, 0, None, fake, None, fake, 1 << 20, None, None)
+    assert lib.fmms_sample_logprobs(None, None, None, 0, 10, 8, 1, 1, 0, 0, 0, *rest, fake, None) == _lib.ERR_BAD_ARG
+    assert lib.fmms_sample_logprobs(*base, 0, *rest, None, None) == _lib.ERR_BAD_ARG
+    assert lib.fmms_sample_logprobs(*base, _lib.FLAG_TWO_STAGE, *rest, fake, None) == _lib.ERR_UNSUPPORTED
+    assert lib.fmms_sample(*base, _lib.FLAG_LOGPROB, *rest) == _lib.ERR_BAD_ARG  # the flag needs the outputs
+    # the workspace head (CTA counter and log-sum-exp scratch) is part of every size
+    assert _lib.query_workspace(10, 8, 1, 1) >= 256 + (16 + 160) * 256 * 8
 
 
 @pytest.mark.parametrize("V,D", [(151936, 4096), (128256, 8192), (262208, 5376), (16032, 8192), (32776, 5376), (100, 16), (513, 64)])
