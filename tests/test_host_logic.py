@@ -139,3 +139,29 @@ def test_reference_import_names_resolve_through_the_shim():
         sys.path.pop(0)
         for m in [k for k in sys.modules if k.startswith("fused_mm_sampling")]:
             del sys.modules[m]
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(lib, tmp_path):
+    """A C89-style consumer (tests/c_abi/consumer.c) compiled with gcc against the header and the
+    shared library: the drop-in boundary must not need C++ or torch."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    from flashsampling_b200 import _lib
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc on this machine")
+    root = Path(__file__).resolve().parent.parent
+    exe = tmp_path / "consumer"
+    libdir = _lib.LIB_PATH.parent
+    subprocess.run(
+        [gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", str(root / "include"),
+         str(root / "tests" / "c_abi" / "consumer.c"), "-o", str(exe), "-L", str(libdir), "-lfmms_b200",
+         f"-Wl,-rpath,{libdir}"],
+        check=True, capture_output=True, text=True,
+    )
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, (res.returncode, res.stdout, res.stderr)
+    assert "c-abi ok" in res.stdout
