@@ -15,6 +15,8 @@ kernels against.  It restates, in plain torch/numpy on the CPU,
   index,
 * the chi-square goodness-of-fit protocol of
   src/fused_mm_sampling/testing.py:178-206,
+* the second stage of its top-k/top-p path (tl_fused_mm_topk.py:76-107), ahead of
+  a CUDA epilogue for it (no kernel uses it yet),
 
 and, for seeded sampling, the counter-based noise stream of the CUDA kernels
 themselves (Philox-4x32-10 keyed by global coordinates), so that a seeded GPU
@@ -272,6 +274,37 @@ def log_probs(logits: torch.Tensor, temperature, ids: torch.Tensor):
     z = logits.double() / (t[:, None] if t.numel() > 1 else t)
     lse = torch.logsumexp(z, dim=-1)
     return z.gather(1, ids.long()) - lse[:, None], lse
+
+
+def topk_topp_probs(logits: torch.Tensor, temperature: float, top_k: int, top_p: float | None = None):
+    """Candidates and probabilities of the reference's top-k/top-p path.
+
+    Follows src/fused_mm_sampling/tl_fused_mm_topk.py: logits / T in fp32 (:213),
+    the k largest per row in descending order with their ids (:87-88, the merge of
+    the per-tile lists is a global top-k), softmax over those k (:91), and for
+    ``top_p`` the nucleus mask ``cumsum - p >= top_p`` that always keeps the most
+    probable token, followed by renormalisation (:93-98).  Returns (ids [B, k],
+    probabilities [B, k]).
+    """
+    z = logits.float() / temperature
+    vals, ids = z.topk(top_k, dim=-1)
+    probs = vals.softmax(dim=-1)
+    if top_p is not None:
+        cumsum = torch.cumsum(probs, dim=-1)
+        mask = (cumsum - probs) >= top_p
+        mask[:, 0] = False
+        probs = probs.masked_fill(mask, 0.0)
+        probs = probs / probs.sum(dim=-1, keepdim=True)
+    return ids, probs
+
+
+def topk_topp_sample(logits, temperature, top_k, top_p, num_samples: int, seed: int | None = None):
+    """``torch.multinomial`` over ``topk_topp_probs`` (tl_fused_mm_topk.py:101-107)."""
+    ids, probs = topk_topp_probs(logits, temperature, top_k, top_p)
+    if seed is not None:
+        torch.manual_seed(seed)
+    picks = torch.multinomial(probs, num_samples=num_samples, replacement=True)
+    return ids.gather(dim=-1, index=picks)
 
 
 def weight_read_time_us(vocab: int, hidden: int, tb_per_s: float = 8.0) -> float:

@@ -134,3 +134,26 @@ def test_bsz_h_table_recorded(golden):
     kernels here plan their tiles in fmms_plan (see test_host_logic.py)."""
     table = dict(zip(golden["bsz_h_in"].tolist(), golden["bsz_h_out"].tolist()))
     assert (table[1], table[16], table[17], table[32], table[33], table[64], table[65]) == (16, 16, 32, 32, 64, 64, 64)
+
+
+def test_topk_topp_oracle_matches_reference_merge():
+    """The reference's own top-k/top-p second stage, run on exact per-tile top-k lists
+    (tests/golden/make_golden_topk.py), against the oracle's restatement on the full logits."""
+    from pathlib import Path
+
+    data = np.load(Path(__file__).resolve().parent / "golden" / "reference_topk_golden.npz")
+    n = 0
+    while f"case{n}_logits" in data:
+        logits = torch.from_numpy(data[f"case{n}_logits"])
+        V, H, k, top_p, temp, seed, draws = data[f"case{n}_params"].tolist()
+        got = O.topk_topp_sample(logits, temp, int(k), None if top_p < 0 else top_p, int(draws), seed=int(seed))
+        want = torch.from_numpy(data[f"case{n}_samples"])
+        assert torch.equal(got, want), f"case {n}"
+        ids, probs = O.topk_topp_probs(logits, temp, int(k), None if top_p < 0 else top_p)
+        assert ids.shape == (int(H), int(k)) and torch.allclose(probs.sum(-1), torch.ones(int(H)))
+        if top_p >= 0:  # the kept prefix holds at least top_p of the top-k mass, and no more tokens than needed
+            full = (logits / temp).topk(int(k), dim=-1).values.softmax(-1)
+            kept = probs > 0
+            assert bool(((full * kept).sum(-1) >= min(top_p, 1.0) - 1e-6).all())
+        n += 1
+    assert n == 4
