@@ -425,6 +425,7 @@ def run_b200(args):
             "note": "the step with return_logprobs=True (log-probability of every sampled id from the same pass) and the "
                     "plain step, alternating call by call inside one timed window (same per-call protocol as `value`)",
         }} if "pair_logprob_ms" in main else {}),
+        "env": {"gpu": torch.cuda.get_device_name(device), "torch": torch.__version__, "cuda": torch.version.cuda},
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
