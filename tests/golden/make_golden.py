@@ -15,7 +15,7 @@ What is recorded
 * make_synthetic_inputs(V, n_hidden_states) for V in {100, 256, 512} x {1, 2}:
   weights, hidden states (bf16 bit patterns) and the exact logits;
 * sample(...) token ids for fixed seeds on those inputs and on a small
-  Qwen-shaped Gaussian head, plus on BASELINE config 1 itself
+  Qwen-shaped Gaussian head, plus on the benchmark's CPU-runnable configuration itself
   (V=151936, d=4096, B=4, fp32 hidden states, T=1);
 * greedy_sample(...) ids, the bsz_h table, shard_weights row ranges and
   _local_reduce on random candidates.
@@ -55,7 +55,7 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
 
 
 def gaussian_head(vocab: int, hidden: int, batch: int, w_std: float, seed: int, hidden_dtype):
-    """Seeded inputs shaped like an LM head (used for configs 0/1 of the benchmark spec)."""
+    """Seeded inputs shaped like an LM head (the small and the CPU-runnable benchmark configurations)."""
     g = torch.Generator().manual_seed(seed)
     w = (torch.randn(vocab, hidden, generator=g) * w_std).bfloat16()
     h = torch.randn(batch, hidden, generator=g).to(hidden_dtype)
@@ -63,7 +63,9 @@ def gaussian_head(vocab: int, hidden: int, batch: int, w_std: float, seed: int, 
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     core, rtesting, TPInfo = import_reference(ref_root)
     cpu = torch.device("cpu")
     out: dict[str, np.ndarray] = {}
@@ -87,7 +89,7 @@ def main():
     out["small_w_checksum"] = np.array([w.double().sum().item(), w.double().abs().sum().item()])
     out["small_h_checksum"] = np.array([h.double().sum().item(), h.double().abs().sum().item()])
 
-    # --- BASELINE config 1: Qwen3-8B-shaped head on the CPU ------------------------
+    # --- the CPU-runnable benchmark configuration: Qwen3-8B-shaped head ---------------
     w, h = gaussian_head(151936, 4096, 4, 0.02, seed=0, hidden_dtype=torch.float32)
     w32 = w.float()
     out["cfg1_sample_seed0_T1"] = core.sample(w32, h, 1, torch.tensor(1.0), seed=0).numpy().copy()

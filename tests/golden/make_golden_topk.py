@@ -39,7 +39,9 @@ def per_tile_topk(scaled_logits: torch.Tensor, top_k: int, tile: int = 128):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden_topk.py /path/to/reference")
+    ref_root = sys.argv[1]
     import_reference(ref_root)
     import fused_mm_sampling.tl_fused_mm_topk as rtopk
 

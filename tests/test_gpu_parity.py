@@ -206,7 +206,7 @@ def test_vocab_offset_shifts_ids_and_noise(fs):
 
 
 def test_qwen_head_full_size_external_noise(fs):
-    """BASELINE config 2 shape (V=151936, d=4096, T=0.7) at B=4 (weight-streaming kernel) and B=64
+    """The headline benchmark shape (Qwen3-8B head: V=151936, d=4096, T=0.7) at B=4 (weight-streaming kernel) and B=64
     (tensor-core kernel) against the fp32 CPU oracle with the same noise."""
     V, D = 151936, 4096
     w, h = _head(V, D, 64, w_std=0.02, seed=0)

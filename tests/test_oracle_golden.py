@@ -44,7 +44,7 @@ def test_oracle_sample_small_gaussian_head(golden):
 
 
 def test_oracle_config1_qwen_head_on_cpu(golden):
-    """BASELINE config 1: V=151936, d=4096, B=4, fp32 hidden states, T=1, 1 draw per row."""
+    """The CPU-runnable benchmark configuration: V=151936, d=4096, B=4, fp32 hidden states, T=1, 1 draw per row."""
     w, h = T.gaussian_head(151936, 4096, 4, 0.02, seed=0, hidden_dtype=torch.float32)
     w32 = w.float()
     assert [w32.double().sum().item(), w32.double().abs().sum().item()] == list(golden["cfg1_w_checksum"])
