@@ -226,5 +226,5 @@ def test_logprob_step_replays_inside_a_cuda_graph(fs, kernel, B):
         if kernel == "mma":
             assert torch.equal(lp, eager_lp)  # static tiles, fixed merge order: bit for bit
         else:  # the weight-streaming kernel deals part of its row groups out dynamically
-            torch.testing.assert_close(lp, eager_lp, atol=1e-5, rtol=0)
+            torch.testing.assert_close(lp, eager_lp, atol=1e-4, rtol=0)
     fs.check_status()
