@@ -188,7 +188,7 @@ def fused_mm_sample(
         from .tensor_parallel import get_exchange
 
         exchange = get_exchange(tp, dev)
-        v_begin = exchange.vocab_offset(V)
+        v_begin = exchange.vocab_offset(V, tp)
     out = torch.empty((B, num_samples), dtype=torch.int64, device=dev)
     need_vals = return_values or tp.size > 1
     vals = torch.empty((B, num_samples), dtype=torch.float32, device=dev) if need_vals else None

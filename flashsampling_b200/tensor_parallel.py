@@ -86,14 +86,46 @@ def reduce_gathered_logprobs(exchange, ids, vals, logprobs, lse):
     )
 
 
+def shard_offset(tp: TPInfo, v_local: int, state: dict, group=None) -> int:
+    """Global vocabulary id of row 0 of this rank's block of ``v_local`` rows.
+
+    With ``tp.vocab_size`` set, the block is ``tp.shard_rows()`` (the last rank also holds the
+    ``vocab_size % size`` remainder rows) and ``v_local`` must match it.  Without it the blocks
+    are taken to be equal, as the reference shards them (testing.py:96-104): offset
+    ``rank * v_local``.  That assumption is verified once, on the first call of an exchange -
+    where all ranks are present anyway because the exchange was just created collectively - by
+    gathering every rank's block size; unequal blocks raise on every rank instead of silently
+    sampling with wrong ids and noise keys.
+    """
+    if tp.vocab_size is not None:
+        begin, end = tp.shard_rows()
+        if end - begin != v_local:
+            raise ValueError(
+                f"rank {tp.rank}: weights have {v_local} rows but its block of a {tp.vocab_size}-row "
+                f"vocabulary over {tp.size} ranks has {end - begin}"
+            )
+        return begin
+    if not state.get("equal_blocks_checked"):
+        sizes: list = [None] * tp.size
+        dist.all_gather_object(sizes, int(v_local), group=group)
+        state["equal_blocks_checked"] = True
+        if any(n != sizes[0] for n in sizes):
+            raise ValueError(
+                f"vocabulary blocks differ across ranks ({sizes}): pass TPInfo(rank, size, vocab_size=V) "
+                "so that every rank knows where its block starts"
+            )
+    return tp.rank * v_local
+
+
 class CollectiveExchange:
     """all_gather through torch.distributed (NCCL baseline on GPUs, gloo on CPU)."""
 
     def __init__(self, tp: TPInfo, device: torch.device, group=None):
         self.tp, self.device, self.group = tp, device, group
+        self._offset_state: dict = {}
 
-    def vocab_offset(self, v_local: int) -> int:
-        return self.tp.rank * v_local
+    def vocab_offset(self, v_local: int, tp: TPInfo | None = None) -> int:
+        return shard_offset(tp or self.tp, v_local, self._offset_state, self.group)
 
     def reduce(self, ids: torch.Tensor, vals: torch.Tensor):
         world = self.tp.size
@@ -148,9 +180,10 @@ class PeerExchange:
             self.ptrs = ptrs
         dist.barrier()  # every rank has mapped every buffer before the first step
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._offset_state: dict = {}
 
-    def vocab_offset(self, v_local: int) -> int:
-        return self.tp.rank * v_local
+    def vocab_offset(self, v_local: int, tp: TPInfo | None = None) -> int:
+        return shard_offset(tp or self.tp, v_local, self._offset_state)
 
     def next_epoch(self) -> int:
         """0 = the step number lives in the exchange buffer and the kernels advance it themselves,
@@ -198,8 +231,8 @@ class _UnfusedView:
         self.inner = inner
         self.max_items = inner.max_items
 
-    def vocab_offset(self, v_local: int) -> int:
-        return self.inner.vocab_offset(v_local)
+    def vocab_offset(self, v_local: int, tp: TPInfo | None = None) -> int:
+        return self.inner.vocab_offset(v_local, tp)
 
     def reduce(self, ids, vals):
         return self.inner.reduce(ids, vals)

@@ -30,10 +30,17 @@ class SyntheticInputs:
     hidden_size: int
 
 
-def shard_weights(weights: torch.Tensor, tp: TPInfo) -> torch.Tensor:
-    """Contiguous vocabulary block of ``tp.rank`` (testing.py:96-104)."""
+def shard_weights(weights: torch.Tensor, tp: TPInfo, keep_remainder: bool = False) -> torch.Tensor:
+    """Contiguous vocabulary block of ``tp.rank`` (testing.py:96-104).
+
+    Like the reference, ``V % size`` trailing rows are dropped; ``keep_remainder=True`` gives
+    them to the last rank instead (``TPInfo.shard_rows``; the sampler then needs
+    ``tp.vocab_size``)."""
     if tp.size == 1:
         return weights
+    if keep_remainder:
+        begin, end = tp.shard_rows(weights.shape[0])
+        return weights.narrow(0, begin, end - begin)
     per = weights.shape[0] // tp.size
     return weights.narrow(0, tp.rank * per, per)
 

@@ -23,6 +23,10 @@ class TPInfo:
 
     rank: int
     size: int
+    # Total vocabulary (extension; the reference's record has only rank and size).  Needed only
+    # when the blocks are unequal, i.e. vocab_size % size != 0: the sampler then takes the global id
+    # of the local block's first row from shard_rows() instead of assuming rank * V_local.
+    vocab_size: int | None = None
 
     def is_rank0(self) -> bool:
         return self.rank == 0
@@ -32,16 +36,20 @@ class TPInfo:
             print(*args, **kwargs)
 
     @classmethod
-    def from_world(cls) -> "TPInfo":
-        return cls(rank=dist.get_rank(), size=dist.get_world_size())
+    def from_world(cls, vocab_size: int | None = None) -> "TPInfo":
+        return cls(rank=dist.get_rank(), size=dist.get_world_size(), vocab_size=vocab_size)
 
-    def shard_rows(self, vocab_size: int) -> tuple[int, int]:
+    def shard_rows(self, vocab_size: int | None = None) -> tuple[int, int]:
         """[begin, end) of this rank's contiguous vocabulary block.
 
         Blocks have ``vocab_size // size`` rows (testing.py:96-104); unlike the
         reference, which drops ``vocab_size % size`` trailing rows, the last
         rank also takes the remainder.
         """
+        if vocab_size is None:
+            vocab_size = self.vocab_size
+        if vocab_size is None:
+            raise ValueError("shard_rows needs the total vocabulary size")
         per = vocab_size // self.size
         begin = self.rank * per
         end = vocab_size if self.rank == self.size - 1 else begin + per

@@ -35,6 +35,29 @@ def _tp_worker(world, seed):
     dist.all_gather(gathered, ids)
     assert all(torch.equal(g, ids) for g in gathered)
 
+    # a vocabulary that does not divide by the world size: the last rank holds the remainder rows
+    # and every rank takes its offset from the total size carried by TPInfo
+    V = 1024 + world - 1
+    w, h = gaussian_head(V, D, B, 0.2, seed=seed + 1)
+    noise = O.kernel_noise(seed, S, B, 0, V)
+    full_idx, _, full_val = O.gumbel_argmax(O.logits_fp32(w, h), 0.9, noise)
+    tpv = TPInfo.from_world(vocab_size=V)
+    lo, hi = tpv.shard_rows()
+    w_local = shard_weights(w, tpv, keep_remainder=True)
+    assert w_local.shape[0] == hi - lo and (tp.rank < world - 1 or hi == V)
+    loc_idx, _, loc_val = O.gumbel_argmax(O.logits_fp32(w_local, h), 0.9, noise[:, :, lo:hi])
+    ex2 = CollectiveExchange(tpv, torch.device("cpu"))
+    assert ex2.vocab_offset(hi - lo, tpv) == lo
+    ids, vals = ex2.reduce(loc_idx + ex2.vocab_offset(hi - lo, tpv), loc_val)
+    assert torch.equal(ids, full_idx) and torch.equal(vals, full_val)
+    # the same unequal blocks without the total size: refused on every rank, not silently mis-keyed
+    ex3 = CollectiveExchange(tp, torch.device("cpu"))
+    with pytest.raises(ValueError, match="vocab_size"):
+        ex3.vocab_offset(hi - lo, tp)
+    # and a block size that contradicts the declared total
+    with pytest.raises(ValueError):
+        ex2.vocab_offset(hi - lo + 1, tpv)
+
 
 @pytest.mark.parametrize("world", [2, 4])
 def test_vocab_sharded_draw_equals_unsharded_draw_gloo(world):
