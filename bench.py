@@ -13,8 +13,13 @@ barrier + synchronize, one pair of CUDA events per step on the launching stream
 (a read-only sweep evicts L2 before each step and the weight copy is rotated),
 maximum over ranks per step, median over the K steps.  The same K steps run
 back to back between one event pair, and the reference's own protocol (a 256 MB
-buffer zeroed before each call), are reported beside it.  One JSON line is
-printed by rank 0.
+buffer zeroed before each call), are reported beside it.  With N > 1 every rank
+first checks that the sharded step returns exactly the ids of the unsharded step
+on the full weight (same seed), and the run fails otherwise.  On one GPU the
+reference's own Triton kernel, when an installed copy of the reference is found
+under baseline/_ref, is timed in a child process on the same inputs and both
+protocols (`reference_triton_us` in the sweep).  One JSON line is printed by
+rank 0.
 """
 
 from __future__ import annotations
@@ -23,9 +28,11 @@ import argparse
 import json
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
+import types
 from pathlib import Path
 
 import torch
@@ -43,6 +50,12 @@ WORKLOADS = {
 }
 SWEEP_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 METRIC = "fused_sample_us_per_step"
+
+
+def workload_label(wl, B, world):
+    """One string for both arms, so that their `config.workload` compare equal."""
+    return (f"{wl['label']}: V={wl['V']} d={wl['D']} bf16, B={B}, {wl['S']} draw(s)/row, T={wl['temp']}, "
+            f"vocabulary sharded over {world} GPU(s)")
 
 
 def algorithmic_bytes(V, D, B, S):
@@ -195,7 +208,7 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     build.build_library()
-    tp = TPInfo(rank=rank, size=world)
+    tp = TPInfo(rank=rank, size=world, vocab_size=WORKLOADS[args.workload]["V"])
     wl = WORKLOADS[args.workload]
     V, D, S = wl["V"], wl["D"], wl["S"]
     # multi-GPU steps are short: a longer sweep keeps the host's launches ahead of the GPU
@@ -244,6 +257,25 @@ def run_b200(args):
         step()
         fs.check_status()
         path = fs.last_path()
+        tp_equal = None
+        if world > 1 and with_e2e:
+            # Correctness of the sharded step on this very workload, before anything is timed: the noise is
+            # keyed by global vocabulary ids, so the ids must equal, bit for bit, those of the unsharded
+            # step on the full weight with the same seed - on every rank.
+            w_full, _, _ = make_inputs(wl, B, 0, 1, device)
+            ok = True
+            for chk_seed in (900001, 900101):
+                want = fs.fused_mm_sample(w_full, h, S, t, seed=chk_seed)
+                got = fs.fused_mm_sample(w, h, S, t, seed=chk_seed, tp=tp)
+                ok = ok and bool(torch.equal(want, got))
+            fs.check_status()
+            del w_full
+            torch.cuda.empty_cache()
+            flag = torch.tensor([1.0 if ok else 0.0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            tp_equal = bool(flag.item() == 1.0)
+            if not tp_equal:
+                raise SystemExit(f"rank {rank}: tensor-parallel ids differ from the unsharded ids (local check: {ok})")
         with ClockSampler(local_rank) as clk:
             times, wall = time_steps(step, steps, warmup, sweep_read, barrier)
         times = reduce_max(times)
@@ -338,18 +370,19 @@ def run_b200(args):
                 ms = reduce_max([r0.elapsed_time(r1)])[0] / graph_steps
                 best = ms if best is None or ms < best else best
         region_ms = best
-        remeasured = False
+        remeasured = None
         if statistics.median(times) > 1.2 * region_ms:
             # The per-call window was far slower than the same steps replayed back to back: a transient
-            # (clock or power event, a neighbour on the host).  Take the per-call measurement once more.
+            # (clock or power event, a neighbour on the host).  The per-call measurement is taken once
+            # more and replaces the first; both medians are reported.
             again, _ = time_steps(step, steps, 3, sweep_read, barrier)
             again = reduce_max(again)
-            if statistics.median(again) < statistics.median(times):
-                times = again
-            remeasured = True
+            remeasured = {"first_us": round(statistics.median(times) * 1e3, 3),
+                          "remeasured_us": round(statistics.median(again) * 1e3, 3)}
+            times = again
         res = dict(B=B, path=path, times_ms=times, ref_times_ms=ref_times, wall_s=wall, clocks=clk.summary(),
                    clocks_region=clk_region.summary(), n_copies=n_copies, region_ms=region_ms, region_kind=region_kind, remeasured=remeasured,
-                   **pair)
+                   tp_equal=tp_equal, **pair)
         fs.check_status()
         del w, h, t, ws
         torch.cuda.empty_cache()
@@ -368,6 +401,21 @@ def run_b200(args):
                               tflops=round(2.0 * V * D * b / (us * 1e-6) / 1e12, 1),
                               back_to_back_us=round(r["region_ms"] * 1e3, 2), remeasured=r["remeasured"],
                               write_flush_us=round(statistics.median(r["ref_times_ms"]) * 1e3, 2)))
+
+    triton_ref = None
+    if world == 1 and args.reference_triton:
+        torch.cuda.empty_cache()
+        batches = [e["B"] for e in sweep] if sweep else [B]
+        triton_ref = reference_triton_sweep(args, batches, max(10, args.steps // 8))
+        for e in sweep:
+            r = triton_ref.get(e["B"]) if "unavailable" not in triton_ref else None
+            if r and "us" in r:
+                e["reference_triton_us"] = r["us"]
+                e["reference_triton_write_flush_us"] = r["write_flush_us"]
+                e["speedup_vs_reference_triton"] = round(r["us"] / e["us"], 3)
+            elif r:
+                e["reference_triton_us"] = None
+                e["reference_triton_unavailable"] = r.get("unavailable")
 
     if rank != 0:
         if world > 1:
@@ -400,8 +448,7 @@ def run_b200(args):
         "dtype": "bf16",
         "data": "synthetic",
         "config": {
-            "workload": f"{wl['label']}: V={V} d={D} bf16, B={B}, {S} draw(s)/row, T={wl['temp']}, "
-                        f"vocabulary sharded over {world} GPU(s)",
+            "workload": workload_label(wl, B, world),
             "batch": B, "vocab": V, "hidden": D, "num_samples": S, "tensor_parallel": world,
             "kernel": main["path"],
             "l2": f"cold: a read-only sweep of a 256 MB buffer evicts L2 before every timed call (no dirty lines), and every "
@@ -426,6 +473,7 @@ def run_b200(args):
                     "plain step, alternating call by call inside one timed window (same per-call protocol as `value`)",
         }} if "pair_logprob_ms" in main else {}),
         "env": {"gpu": torch.cuda.get_device_name(device), "torch": torch.__version__, "cuda": torch.version.cuda},
+        **({"tp_ids_equal_unsharded": main["tp_equal"]} if main["tp_equal"] is not None else {}),
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
@@ -448,6 +496,15 @@ def run_b200(args):
     }
     if sweep:
         line["sweep"] = sweep
+    if triton_ref is not None:
+        mine = triton_ref.get(B) if "unavailable" not in triton_ref else None
+        line["reference_triton"] = (
+            {"us": mine["us"], "write_flush_us": mine["write_flush_us"],
+             "note": "the reference's own Triton kernel (fused_mm_sample_triton, installed copy under baseline/_ref) on "
+                     "the same box, inputs and per-call protocols, in a child process; `us` pairs with `value`, "
+                     "`write_flush_us` with `write_flush_protocol_us`"}
+            if mine and "us" in mine else
+            {"unavailable": (mine or triton_ref).get("unavailable", "not measured")})
     if not args.no_cpu and world == 1:
         line["cpu_baseline"] = cpu_baseline(wl, B, budget_s=args.cpu_budget)
     print(json.dumps(line), flush=True)
@@ -455,9 +512,96 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def import_reference_triton():
+    """The reference's own package, from a copy installed under baseline/_ref (kept out of the history;
+    `pip install --no-deps --target baseline/_ref <checkout of the reference>`).  The one module it imports
+    that this image lacks, `nvtx` (range annotations only), is replaced by a no-op stand-in."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "fused_mm_sampling" / "core.py").exists():
+        raise FileNotFoundError("no installed copy of the reference under baseline/_ref")
+    try:
+        import nvtx  # noqa: F401
+    except ImportError:
+        stub = types.ModuleType("nvtx")
+
+        def annotate(*a, **k):
+            if len(a) == 1 and callable(a[0]) and not k:
+                return a[0]
+            return lambda f: f
+
+        stub.annotate = annotate
+        sys.modules["nvtx"] = stub
+    sys.path.insert(0, str(ref))
+    import fused_mm_sampling.core as rcore
+
+    return rcore
+
+
+def run_triton_leg(args):
+    """--triton-leg (child process of the one-GPU benchmark): the reference's Triton kernel
+    `fused_mm_sample_triton` on the same synthetic inputs, per-call CUDA events, both L2 protocols."""
+    from flashsampling_b200 import _lib, build
+
+    build.build_library()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    rcore = import_reference_triton()
+    wl = WORKLOADS[args.workload]
+    S = wl["S"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    lib = _lib.load()
+
+    def sweep_read():
+        lib.fmms_l2_sweep(flush.data_ptr(), flush.numel(), torch.cuda.current_stream().cuda_stream)
+
+    out = []
+    w = None
+    for B in [int(x) for x in args.batches.split(",")]:
+        w_b, h, t = make_inputs(wl, B, 0, 1, device)
+        w = w_b if w is None else w  # the weight does not depend on B
+        del w_b
+        if t.ndim:  # the reference takes one temperature for the whole batch: use the mean
+            t = t.mean()
+        seed = [0]
+
+        def step():
+            seed[0] += S
+            return rcore.fused_mm_sample_triton(w, h, S, t, seed=seed[0])
+
+        entry = {"B": B}
+        try:
+            step()  # compiles and autotunes
+            torch.cuda.synchronize()
+            n = max(10, args.steps)
+            a, _ = time_steps(step, n, 5, sweep_read, lambda: None)
+            b, _ = time_steps(step, n, 5, flush.zero_, lambda: None)
+            entry.update(us=round(statistics.median(a) * 1e3, 2), write_flush_us=round(statistics.median(b) * 1e3, 2))
+        except Exception as exc:  # a shape the reference's kernel refuses: report, go on
+            entry["unavailable"] = f"{type(exc).__name__}: {str(exc)[:200]}"
+        out.append(entry)
+    print(json.dumps({"triton_leg": out}), flush=True)
+
+
+def reference_triton_sweep(args, batches, steps):
+    """Run --triton-leg in a child process (so that a failure of the reference's kernel cannot take the
+    benchmark's CUDA context with it) and return {B: entry}, or {"unavailable": reason}."""
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--triton-leg", "--workload", args.workload,
+           "--batches", ",".join(map(str, batches)), "--steps", str(steps)]
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        for ln in reversed(res.stdout.strip().splitlines()):
+            if ln.startswith("{") and "triton_leg" in ln:
+                return {e["B"]: e for e in json.loads(ln)["triton_leg"]}
+        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or ["no output"]
+        return {"unavailable": f"rc={res.returncode}: {tail[0][:300]}"}
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+
+
 def cpu_baseline(wl, B, budget_s=20.0, steps=None, warmup=1):
     """The reference's torch path (matmul -> /T -> softmax -> multinomial; oracle restatement) on the host
-    cores, on a bounded sample of the workload: the first `rows` vocabulary rows."""
+    cores.  Every step is one full pass over the workload (all V rows, B hidden states); the sample is bounded
+    in the NUMBER of steps: `steps` of them, or as many as fit into `budget_s` seconds (at least 3)."""
     from oracle import fmms_oracle as O
 
     cores = len(os.sched_getaffinity(0))
@@ -492,13 +636,17 @@ def run_reference(args):
         return
     wl = WORKLOADS[args.workload]
     steps = max(1, min(args.steps, 20))
-    base = cpu_baseline(wl, args.batch, steps=steps, warmup=max(1, min(args.warmup, 2)))
+    warmup = max(1, min(args.warmup, 3))
+    base = cpu_baseline(wl, args.batch, steps=steps, warmup=warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "us", "n_gpus": args.gpus,
-        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(base["value"] / 1e3, 4),
+        "steps": steps, "warmup": warmup, "ms_per_step": round(base["value"] / 1e3, 4),
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{wl['label']}: V={wl['V']} d={wl['D']}, B={args.batch}, {wl['S']} draw(s)/row, "
-                               "reference torch path on the host CPU"},
+        "config": {"workload": workload_label(wl, args.batch, args.gpus),
+                   "batch": args.batch, "vocab": wl["V"], "hidden": wl["D"], "num_samples": wl["S"],
+                   "tensor_parallel": args.gpus,
+                   "implementation": "the reference's torch path (matmul, softmax, multinomial) on the host CPU, "
+                                     "fp32 weights; every step is one full pass over the whole workload"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -539,8 +687,14 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--once", action="store_true", help="five calls of one configuration, for profilers")
     ap.add_argument("--kernel", default=None, choices=["gemv", "mma"], help="--once: force a kernel")
+    ap.add_argument("--reference-triton", action=argparse.BooleanOptionalAction, default=True,
+                    help="one GPU: also time the reference's Triton kernel (baseline/_ref) in a child process")
+    ap.add_argument("--triton-leg", action="store_true", help="child process of --reference-triton")
+    ap.add_argument("--batches", default="64", help="--triton-leg: comma-separated batch sizes")
     args = ap.parse_args()
-    if args.once:
+    if args.triton_leg:
+        run_triton_leg(args)
+    elif args.once:
         run_once(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -286,7 +286,7 @@ static int launch_gemv(DeviceInfo& d, const void* W, SampleParams& p, cudaStream
 
 // ---- tensor-core launch -----------------------------------------------------------
 struct UmmaMaps {
-  CUtensorMap wq, wq1, hm, wt1, wt2, hmt;
+  CUtensorMap wq, wq1, hm;
 };
 
 template <int MT, bool LSE>
@@ -299,8 +299,7 @@ static int launch_umma_mt_lse(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p
     d.umma_attr[LSE][MT] = true;
   }
   umma_sample_kernel<MT, LSE><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
-      mp.wq, mp.wq1, mp.hm, mp.wt1, mp.wt2, mp.hmt, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs,
-      pl.tail1_units, pl.tail2_units, pl.tail_slabs);
+      mp.wq, mp.wq1, mp.hm, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
@@ -316,14 +315,14 @@ static int umma_slabs_force() {
   return v;
 }
 
-static int umma_tails() {
-  static const int v = env_int("FMMS_UMMA_TAILS");  // 0 (default): off; 1: 64- and 32-row closing tiles; 2: 64-row only
+static int umma_copies_cap() {
+  static const int v = env_int("FMMS_UMMA_COPIES");  // 0 (default): no row replicas; 2 / 4: up to that many
   return v;
 }
 
 static int build_umma_maps(const void* W, const void* H, const SampleParams& p, const UmmaPlan& pl, UmmaMaps* mp) {
   int rc;
-  if (pl.slabs > 1 || pl.tail1_units) {
+  if (pl.slabs > 1) {
     rc = get_tensor_map_slabs(W, p.V, p.D, pl.q_units * 16, pl.slabs, &mp->wq);
     if (rc != kOk) return rc;
     mp->wq1 = mp->wq;
@@ -344,32 +343,29 @@ static int build_umma_maps(const void* W, const void* H, const SampleParams& p, 
     rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->hm);
     if (rc != kOk) return rc;
   }
-  mp->wt1 = mp->wt2 = mp->wq;
-  mp->hmt = mp->hm;
-  if (pl.tail1_units) {
-    rc = get_tensor_map_slabs(W, p.V, p.D, pl.tail1_units * 16, pl.tail_slabs, &mp->wt1);
-    if (rc != kOk) return rc;
-    rc = get_tensor_map_slabs(W, p.V, p.D, pl.tail2_units * 16, pl.tail_slabs, &mp->wt2);
-    if (rc != kOk) return rc;
-    rc = get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.tail_slabs, &mp->hmt);
-    if (rc != kOk) return rc;
-  }
   return kOk;
 }
 
-static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream) {
+static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream,
+                       size_t cand_capacity) {
+  // Row replicas keep the S > 1 scratch by TMEM lane (128 rows): without room for that, run without them.
+  const int copies_cap = (p.S > 1 && (size_t)128 * p.S > cand_capacity) ? 1 : umma_copies_cap();
   UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
-                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), umma_tails());
+                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), copies_cap);
   if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
   UmmaMaps mp;
   int rc = build_umma_maps(W, H, p, pl, &mp);
-  if (rc != kOk && (pl.slabs > 1 || pl.tail1_units)) {
-    // the driver refused the 3-D view: fall back to one slab per operation, no closing tiles
+  if (rc != kOk && pl.slabs > 1) {
+    // the driver refused the 3-D view: fall back to one slab per operation
     pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(),
-                   umma_min_tiles(), 0, 0, 0);
+                   umma_min_tiles(), 0, 0, copies_cap);
     rc = build_umma_maps(W, H, p, pl, &mp);
   }
   if (rc != kOk) return -rc;
+  if (pl.copies > 1) {
+    p.cand_rows = 128;
+    p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * 128 * p.S);
+  }
   p.stages = pl.stages;
   p.tile_rows = pl.q_units * 16;
   p.tiles_per_cta = pl.tiles_per_cta;
@@ -499,7 +495,10 @@ int fmms_num_sms(int* num_sms) {
 
 int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes) {
   if (!bytes || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
-  *bytes = workspace_bytes_for(B > 256 ? 256 : B, S);
+  // With several draws per row the tensor-core kernel keeps running candidates in the workspace, one
+  // row per TMEM lane (128) when it replicates a batch of at most 64 rows over the lane quadrants.
+  const int rows = B > 256 ? 256 : ((S > 1 && B <= 64) ? 128 : B);
+  *bytes = workspace_bytes_for(rows, S);
   return FMMS_OK;
 }
 
@@ -544,11 +543,11 @@ int fmms_plan(int V_local, int D, int B, int S, int flags, int num_sms, int max_
       plan[7] = pp.grid * kUmmaEpiGroups;
       return FMMS_OK;
     }
-    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0, umma_tails());
+    const UmmaPlan pl = umma_plan(V_local, B, num_sms, max_smem_bytes, 0, 256, 0, 1, D, 0, umma_copies_cap());
     plan[0] = FMMS_PATH_MMA;
     plan[1] = pl.grid;
     plan[2] = pl.q_units * 16;
-    plan[3] = pl.tiles_per_cta + (pl.tail1_units ? 1 : 0) + (pl.tail2_units ? 1 : 0);
+    plan[3] = pl.tiles_per_cta;
     plan[4] = pl.stages;
     plan[5] = pl.mt;
     plan[6] = (int)pl.smem;
@@ -625,8 +624,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
                        float* out_logprob, float* out_lse) {
   const bool greedy = flags & FMMS_FLAG_GREEDY;
   (void)greedy;
-  size_t need = 0;
-  fmms_query_workspace(V_local, D, B, S, &need);
+  const size_t need = workspace_bytes_for(B, S);  // the least that works; fmms_query_workspace may ask for more
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return FMMS_ERR_WORKSPACE;
 
   DeviceInfo* d = nullptr;
@@ -662,6 +660,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
   p.keys = reinterpret_cast<unsigned long long*>(ws + kWsHeadBytes);
   p.cand_val = reinterpret_cast<float*>(ws + kWsHeadBytes + cap * 8);
   p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * B * S);
+  p.cand_rows = B;
   p.out_idx = out_idx;
   p.out_val = out_val;
   p.tp_world = 1;
@@ -702,7 +701,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
     if (use_pair_kernel(V_local, D, B, d->num_sms))
       parts = launch_umma_pair(*d, W_bf16, H_bf16, p, stream);
     else
-      parts = launch_umma(*d, W_bf16, H_bf16, p, stream);
+      parts = launch_umma(*d, W_bf16, H_bf16, p, stream, cap);
     g_last_path = FMMS_PATH_MMA;
   }
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;

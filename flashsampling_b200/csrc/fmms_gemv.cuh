@@ -52,8 +52,9 @@ struct SampleParams {
   unsigned long long* keys;  // [S * B] packed winners, zero on entry and on exit (atomicMax target)
   unsigned int* ticket;      // CTAs-done counter, zero on entry and on exit
   unsigned int* sched;       // dynamic work counter, zero on entry and on exit
-  float* cand_val;           // [2 * gridDim.x, S * B] running per-CTA candidates (tensor-core path, S > 1)
+  float* cand_val;           // [4 * gridDim.x, S * cand_rows] running per-CTA candidates (tensor-core path, S > 1)
   int* cand_idx;
+  int cand_rows;             // rows of that scratch: B, or 128 (TMEM lanes) when the kernel runs row replicas
   long long* out_idx;        // [B, S]
   float* out_val;            // [B, S] or null
   // kFlagLogprob: per-CTA partial log-sum-exps, the rows' normalisers, and the outputs

@@ -17,6 +17,16 @@
 //               scale, noise, running argmax.  TMEM accumulators are multi-buffered
 //               so the epilogue of tile i overlaps the mainloop of tile i+1.
 // Batches above 128 use two M tiles that share every W tile (MT = 2).
+//
+// Row replicas (batches of at most 64 rows).  An epilogue warp can only read its own quadrant of
+// 32 TMEM lanes, so with 64 (32) batch rows half (three quarters) of the epilogue warps - and of
+// the SM's four schedulers - would have no rows.  Instead of one MMA over the whole tile the issuer
+// then runs R = 2 (4) MMAs per K step, each over 1/R of the tile's columns, and shifts the A
+// operand of replica k back by k * 128/R rows: rows k*128/R .. of that operand are the hidden
+// states (the rows before them are whatever precedes the hidden-state tile in the stage, i.e. W
+// bytes; their accumulator lanes are never read).  Replica k's columns therefore hold the batch
+// rows in lanes k*128/R .., and every quadrant scans 1/R of the columns of the same rows.  No
+// extra shared memory, no extra TMA traffic, the same tensor-core work.
 #pragma once
 
 #include <cuda.h>
@@ -46,12 +56,9 @@ struct UmmaPlan {
   int h_rows;         // rows of the hidden-state TMA box (MT = 1: ceil8(B); MT = 2: 128)
   int mt;             // M tiles (1 or 2)
   int slabs;          // 64-column K slabs per pipeline stage (one TMA operation fetches them all)
-  int tail1_units, tail2_units;  // two short closing tiles per CTA (0 = none), see umma_plan
-  int tail_slabs;     // K slabs per stage for the closing tiles
+  int copies;         // row replicas R (1, 2 or 4): MMAs per K step, each over 1/R of the tile's columns
   size_t smem;
 };
-
-constexpr int kTail1Units = 4, kTail2Units = 2;  // closing tiles of 64 and 32 rows
 
 // Shared memory: [barriers 1 KiB][stages x (W tile: tallest tile x 128 B | MT hidden-state tiles:
 // h_rows x 128 B)][16 KiB slack].  With fewer than 128 hidden-state rows the MMA's 128-row A
@@ -60,12 +67,6 @@ constexpr int kTail1Units = 4, kTail2Units = 2;  // closing tiles of 64 and 32 r
 __host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows, int slabs) {
   return (size_t)slabs * ((size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128);
 }
-// with closing tiles: the stage must also hold tail_slabs x (64 rows of W + the hidden-state slab)
-__host__ __device__ inline size_t umma_stage_bytes_tail(int mt, int q_units, int h_rows, int slabs, int tail_slabs) {
-  const size_t big = umma_stage_bytes(mt, q_units, h_rows, slabs);
-  const size_t tail = (size_t)tail_slabs * ((size_t)kTail1Units * 16 * 128 + (size_t)mt * h_rows * 128);
-  return big > tail ? big : tail;
-}
 
 // Work split.  The vocabulary is dealt out in units of 16 rows: CTA c gets a contiguous range
 // of U_c = units_total / grid (+1 for the first units_total % grid CTAs) units and cuts it into
@@ -73,7 +74,7 @@ __host__ __device__ inline size_t umma_stage_bytes_tail(int mt, int q_units, int
 // CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
                                    int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1, int D = 0, int slabs_force = 0,
-                                   int tails = 0) {
+                                   int copies_cap = 0) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
@@ -84,21 +85,6 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
   int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
-  // Closing tiles (off by default).  The epilogue of a tile (Philox + two logarithms per element,
-  // all rows of a TMEM lane quadrant on ONE scheduler) takes ~10 us for 208 columns and only the
-  // last one is exposed.  Ending every CTA's range with a 64-row (and a 32-row) tile shortens the
-  // exposed epilogue to ~4 us, but measured slower overall (Qwen head, B = 64: 213-220 us against
-  // 201 us): the short tiles' mainloops run well below the streaming rate and the previous big
-  // tile's epilogue still has to finish first.
-  pl.tail1_units = pl.tail2_units = 0;
-  pl.tail_slabs = 1;
-  if (tails && pl.mt == 1 && D > 0 && D % 64 == 0 && pl.h_rows <= 64 && u_max >= 24 && nt_target == 0 &&
-      min_tiles <= 1) {
-    pl.tail1_units = kTail1Units;
-    pl.tail2_units = tails == 1 ? kTail2Units : 0;  // tails == 2: one closing tile only
-    pl.tail_slabs = D / 64 < 4 ? D / 64 : 4;
-    u_max -= pl.tail1_units + pl.tail2_units;  // what remains for the big tiles
-  }
   int cap_units = pl.nt_cap / 16;
   if (pl.mt == 1 && pl.h_rows <= 64 && D > 0 && D % 64 == 0) {
     // keep tiles low enough for two K slabs per stage and three stages (the 52 KiB operations
@@ -130,54 +116,65 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
     while (sk > 1 && min_stages * umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, sk) + fixed > (size_t)max_smem) --sk;
     pl.slabs = sk;
   }
-  const size_t sb = pl.tail1_units ? umma_stage_bytes_tail(pl.mt, pl.q_units, pl.h_rows, pl.slabs, pl.tail_slabs)
-                                   : umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, pl.slabs);
+  const size_t sb = umma_stage_bytes(pl.mt, pl.q_units, pl.h_rows, pl.slabs);
   int stages = stages_cap > 1 ? stages_cap : kUmmaMaxStages;
   if (stages > kUmmaMaxStages) stages = kUmmaMaxStages;
   while (stages > 2 && stages * sb + fixed > (size_t)max_smem) --stages;
   pl.stages = stages;
   pl.smem = stages * sb + fixed;
+  // Row replicas: the A operand of replica k starts k * (16 KiB / R) bytes before the hidden-state
+  // slab, which must still lie inside the stage: the W slabs in front of it have to be that long
+  // even for the lower of the two tile heights.
+  // Off unless asked for (copies_cap = 2 or 4): measured on the Qwen head, B = 64, the epilogue of a
+  // tile drops from 9.5 to 4.9 (2.8) us with 2 (4) replicas, but every MMA re-reads its 128-row A
+  // operand, and the mainloop slows from 171 to 236 (344) us.
+  int r = 1;
+  if (pl.mt == 1 && copies_cap >= 2) {
+    r = pl.h_rows <= 32 ? 4 : (pl.h_rows <= 64 ? 2 : 1);
+    if (r > copies_cap) r = 2;
+  }
+  const int low_units = pl.q_units > 1 ? pl.q_units - 1 : pl.q_units;
+  while (r > 1 && (size_t)pl.slabs * low_units * 16 * 128 < (size_t)(r - 1) * (16384 / r)) r >>= 1;
+  pl.copies = r;
   return pl;
 }
 
 // The tile schedule of one CTA, recomputed identically by every warp role.
 struct TileInfo {
-  int v0;    // first vocabulary row
-  int nt;    // rows (0: nothing, skip)
-  int kind;  // 0 = big tile, 1 / 2 = first / second closing tile
+  int v0;  // first vocabulary row
+  int nt;  // rows (0: nothing, skip)
 };
 
 struct TileWalk {
   int u_next;  // first unit of the next tile
-  int base, extra, i, T, tail1, tail2;
-  __device__ __forceinline__ TileWalk(int units_total, int T_, int tail1_, int tail2_) {
+  int base, extra, i, T;
+  __device__ __forceinline__ TileWalk(int units_total, int T_) {
     const int per = units_total / (int)gridDim.x, rem = units_total % (int)gridDim.x;
     const int c = blockIdx.x;
     const int u_cnt = per + (c < rem ? 1 : 0);
     u_next = c * per + min(c, rem);
     T = T_;
-    tail1 = tail1_;
-    tail2 = tail2_;
-    const int big = u_cnt - tail1 - tail2;  // the planner only enables closing tiles when big > 0
-    base = big / T;
-    extra = big % T;
+    base = u_cnt / T;
+    extra = u_cnt % T;
     i = 0;
   }
-  __device__ __forceinline__ int count() const { return T + (tail1 ? 1 : 0) + (tail2 ? 1 : 0); }
+  __device__ __forceinline__ int count() const { return T; }
   __device__ __forceinline__ TileInfo next() {
-    int units, kind = 0;
-    if (i < T) {
-      units = base + (i < extra ? 1 : 0);
-    } else {
-      kind = i - T + 1;
-      units = kind == 1 ? tail1 : tail2;
-    }
-    TileInfo t{u_next * 16, units * 16, kind};
+    const int units = base + (i < extra ? 1 : 0);
+    TileInfo t{u_next * 16, units * 16};
     u_next += units;
     ++i;
     return t;
   }
 };
+
+// Columns [begin, end) of a tile of `nt` rows (a multiple of 16) that replica k of R scans:
+// the tile's 16-row units dealt out as evenly as possible.
+__device__ __forceinline__ void replica_columns(int nt, int R, int k, int& begin, int& end) {
+  const int units = nt >> 4, per = units / R, rem = units % R;
+  begin = (k * per + min(k, rem)) * 16;
+  end = begin + (per + (k < rem ? 1 : 0)) * 16;
+}
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -244,6 +241,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// CW (16 or 32) accumulator columns of the warp's 32 lanes, starting at TMEM address taddr
+template <int CW>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[CW]) {
+  if constexpr (CW == 32) tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
+}
+
 // ---- epilogue scan shared by the tensor-core kernels ---------------------------------------
 struct EpiRow {
   int b;          // batch row this thread owns
@@ -255,25 +270,26 @@ struct EpiRow {
 };
 
 // kFlagLogprob: fold the scaled logits of columns [c_begin, c_end) of the accumulator tile into
-// the thread's running log-sum-exp - one maximum and one rescale per 32-column chunk.  A pass of
+// the thread's running log-sum-exp - one maximum and one rescale per CW-column chunk.  A pass of
 // its own over the tile (TMEM reads are cheap), so that the sampling scan keeps its registers.
+template <int CW = 32>
 __device__ __forceinline__ void lse_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
                                                  int c_begin, int c_end, int v0, float& lse_m, float& lse_l) {
   const float sc = e.inv_t * kLog2e;  // > 0: the largest logit gives the largest scaled logit
-  for (int c = c_begin; c < c_end; c += 32) {
-    uint32_t acc[32];
-    tmem_ld32(t_addr + (uint32_t)c, acc);
+  for (int c = c_begin; c < c_end; c += CW) {
+    uint32_t acc[CW];
+    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
     if (e.row_ok) {
       const int n_ok = min(c_end - c, p.V - (v0 + c));  // valid columns of this chunk
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < CW; ++i)
         if (i < n_ok) mx = fmaxf(mx, __uint_as_float(acc[i]));
       if (mx > -INFINITY) {
         const float mn = fmaxf(lse_m, mx * sc);
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int i = 0; i < CW; i += 2) {
           if (i < n_ok) sum0 += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
           if (i + 1 < n_ok) sum1 += ex2_approx(fmaf(__uint_as_float(acc[i + 1]), sc, -mn));
         }
@@ -287,22 +303,23 @@ __device__ __forceinline__ void lse_tile_columns(const SampleParams& p, const Ep
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
 // quadrant, first column of the tile) for draw `s`: scale, add noise, keep the running (max, id)
 // of the thread's row.  The tile's first column is vocabulary row v0 of this shard.
+template <int CW = 32>
 __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
                                                   int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
-  for (int c = c_begin; c < c_end; c += 32) {
-    uint32_t acc[32];
-    tmem_ld32(t_addr + (uint32_t)c, acc);
+  for (int c = c_begin; c < c_end; c += CW) {
+    uint32_t acc[CW];
+    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
     if (e.row_ok) {
       const int vbase = v0 + c;
       if (e.ret_logits && s == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < CW; ++i)
           if (c + i < c_end && vbase + i < p.V)
             p.logits_out[(size_t)e.b * p.V + vbase + i] = __uint_as_float(acc[i]);
       }
       if (e.greedy) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < CW; ++i) {
           const float y = __uint_as_float(acc[i]);
           if (c + i < c_end && vbase + i < p.V && y > bv) {
             bv = y;
@@ -312,7 +329,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
       } else if (e.ext) {
         const float* nz = p.ext_noise + (size_t)s * p.noise_s_stride + (size_t)e.b * p.noise_ld + vbase;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < CW; ++i) {
           if (c + i < c_end && vbase + i < p.V) {
             const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? nz[i] : 0.f);
             if (y > bv) {
@@ -324,7 +341,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
       } else if (e.quad_aligned) {
         const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < CW / 4; ++g) {
           const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -339,7 +356,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < CW; ++i) {
           const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
           const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, vg >> 2);
           const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)) : 0.f);
@@ -353,25 +370,32 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
   }
 }
 
+// Columns [c_begin, c_end) of the range [r_begin, r_end) that column group `g` of `groups` scans:
+// whole CW-column chunks, dealt out evenly.
+template <int CW>
+__device__ __forceinline__ void group_columns(int r_begin, int r_end, int g, int groups, int& c_begin, int& c_end) {
+  const int chunks = (r_end - r_begin + CW - 1) / CW;
+  const int per_group = (chunks + groups - 1) / groups;
+  c_begin = min(r_begin + g * per_group * CW, r_end);
+  c_end = min(c_begin + per_group * CW, r_end);
+}
+
 // ---- the kernel ------------------------------------------------------------------
 template <int MT, bool LSE = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
-                   const __grid_constant__ CUtensorMap h_map, const __grid_constant__ CUtensorMap w_map_t1,
-                   const __grid_constant__ CUtensorMap w_map_t2, const __grid_constant__ CUtensorMap h_map_t,
-                   const SampleParams p, const int nt_cap, const int units_total, const int q_units,
-                   const int h_rows, const int SK, const int tail1, const int tail2, const int SKT) {
+                   const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
+                   const int units_total, const int q_units, const int h_rows, const int SK, const int R_) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
+  const int R = (MT == 1) ? R_ : 1;     // row replicas (see the head of this file)
   // stage = [SK W slabs][MT x SK hidden-state slabs]; SK > 1 means the maps are 3-D (slab = dim 2)
-  // A stage holds `sk` W slabs of the tile (sk * nt * 128 bytes) followed at once by MT x sk
-  // hidden-state slabs; sk is SK for the big tiles and SKT for the closing tiles.
   const size_t h_slab_bytes = (size_t)h_rows * 128;
-  const size_t stage_bytes = tail1 ? umma_stage_bytes_tail(MT, q_units, h_rows, SK, SKT)
-                                   : umma_stage_bytes(MT, q_units, h_rows, SK);
+  const size_t stage_bytes = umma_stage_bytes(MT, q_units, h_rows, SK);
   const int slabs_total = (p.D + kUmmaBK - 1) / kUmmaBK;
+  const int KB = (slabs_total + SK - 1) / SK;  // pipeline steps per tile
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
   smem += 1024;  // stages start 1 KiB-aligned behind the barriers
   uint64_t* empty_bar = full_bar + stages;
@@ -405,7 +429,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   // S > 1 keeps the running candidates of each (row, draw) in global memory: one row per CTA and
   // epilogue warpgroup, which start as "none"
   if (p.S > 1) {
-    const int n = kUmmaEpiGroups * p.S * p.B;
+    const int n = kUmmaEpiGroups * p.S * p.cand_rows;
     float* cv = p.cand_val + (size_t)cta * n;
     int* ci = p.cand_idx + (size_t)cta * n;
     for (int i = tid; i < n; i += kUmmaThreads) {
@@ -435,20 +459,15 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
       int it = 0;
       bool ok = true;
-      TileWalk walk(units_total, n_tiles, tail1, tail2);
-      const int total_tiles = walk.count();
-      for (int t = 0; t < total_tiles && ok; ++t) {
+      TileWalk walk(units_total, n_tiles);
+      const bool flat = (SK == 1);  // one slab per stage: 2-D maps
+      for (int t = 0; t < n_tiles && ok; ++t) {
         const TileInfo ti = walk.next();
         const int v0 = ti.v0, NT = ti.nt;
         if (NT == 0) continue;
-        const int sk = ti.kind ? SKT : SK;
-        const int KB = (slabs_total + sk - 1) / sk;  // pipeline steps of this tile
-        const uint32_t tx = (uint32_t)sk * (is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u);
-        const CUtensorMap* wm = ti.kind == 0 ? ((NT == q_units * 16) ? &w_map_q : &w_map_q1)
-                                             : (ti.kind == 1 ? &w_map_t1 : &w_map_t2);
-        const CUtensorMap* hm = ti.kind == 0 ? &h_map : &h_map_t;
-        const bool flat = (SK == 1 && tail1 == 0);  // one slab per stage and no closing tiles: 2-D maps
-        const size_t h_off = (size_t)sk * NT * 128;   // hidden-state slabs follow the W slabs
+        const uint32_t tx = (uint32_t)SK * (is_w ? (uint32_t)NT * 128u : (uint32_t)MT * (uint32_t)h_rows * 128u);
+        const CUtensorMap* wm = (NT == q_units * 16) ? &w_map_q : &w_map_q1;
+        const size_t h_off = (size_t)SK * NT * 128;   // hidden-state slabs follow the W slabs
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int st = it % stages;
           const uint32_t n = (uint32_t)(it / stages);
@@ -460,13 +479,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           mbar_arrive_expect_tx(&full_bar[st], tx);
           if (is_w) {
             if (flat) tma_load_2d_hint(sw, wm, kb * kUmmaBK, v0, &full_bar[st], pol);
-            else tma_load_3d_hint(sw, wm, 0, v0, kb * sk, &full_bar[st], pol);
+            else tma_load_3d_hint(sw, wm, 0, v0, kb * SK, &full_bar[st], pol);
           } else {
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              uint8_t* dst = sw + h_off + (size_t)m * sk * h_slab_bytes;
-              if (flat) tma_load_2d_hint(dst, hm, kb * kUmmaBK, m * 128, &full_bar[st], pol);
-              else tma_load_3d_hint(dst, hm, 0, m * 128, kb * sk, &full_bar[st], pol);
+              uint8_t* dst = sw + h_off + (size_t)m * SK * h_slab_bytes;
+              if (flat) tma_load_2d_hint(dst, &h_map, kb * kUmmaBK, m * 128, &full_bar[st], pol);
+              else tma_load_3d_hint(dst, &h_map, 0, m * 128, kb * SK, &full_bar[st], pol);
             }
           }
         }
@@ -483,16 +502,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      TileWalk walk(units_total, n_tiles, tail1, tail2);
-      const int total_tiles = walk.count();
-      for (int t = 0, ta = 0; t < total_tiles && ok; ++t) {
+      TileWalk walk(units_total, n_tiles);
+      const uint32_t a_shift = (uint32_t)(16384 / R);  // bytes by which each further replica's A operand starts earlier
+      for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
         const TileInfo ti = walk.next();
         const int NT = ti.nt;
         if (NT == 0) continue;
-        const int sk = ti.kind ? SKT : SK;
-        const int KB = (slabs_total + sk - 1) / sk;
-        const uint32_t h_off = (uint32_t)(sk * NT * 128);
-        const uint32_t idesc = umma_idesc(NT);
+        const uint32_t h_off = (uint32_t)(SK * NT * 128);
         const int j = ta % acc_stages;
         const uint32_t un = (uint32_t)(ta / acc_stages);
         ++ta;
@@ -508,19 +524,38 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           tc_fence_after();
           if (it == 0) stamp(p, 2);
           const uint32_t sw = smem_u32(smem + st * stage_bytes);
-          for (int sl = 0; sl < sk; ++sl) {
+          for (int sl = 0; sl < SK; ++sl) {
             // TMA packs the slabs of a box back to back: the slab pitch follows the tile height
-            const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)(sl * NT * 128));
+            const uint32_t w_slab = sw + (uint32_t)(sl * NT * 128);
+            if (MT == 1) {
+              const uint32_t a_slab = sw + h_off + (uint32_t)(sl * h_slab_bytes);
+              for (int r = 0; r < R; ++r) {
+                int cb, ce;
+                replica_columns(NT, R, r, cb, ce);
+                if (ce == cb) continue;
+                const uint64_t adesc = umma_smem_desc(a_slab - (uint32_t)r * a_shift);
+                const uint64_t bdesc = umma_smem_desc(w_slab + (uint32_t)(cb * 128));
+                const uint32_t idesc = umma_idesc(ce - cb);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap + cb);
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              const uint64_t adesc =
-                  umma_smem_desc(sw + h_off + (uint32_t)((m * sk + sl) * h_slab_bytes));
-              const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
+                for (int k = 0; k < kUmmaBK / 16; ++k)
+                  umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            (kb | sl | k) != 0 ? 1u : 0u);
+              }
+            } else {
+              const uint64_t bdesc = umma_smem_desc(w_slab);
+              const uint32_t idesc = umma_idesc(NT);
 #pragma unroll
-              for (int k = 0; k < kUmmaBK / 16; ++k) {
-                // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
-                umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                          (kb | sl | k) != 0 ? 1u : 0u);
+              for (int m = 0; m < MT; ++m) {
+                const uint64_t adesc =
+                    umma_smem_desc(sw + h_off + (uint32_t)((m * SK + sl) * h_slab_bytes));
+                const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
+#pragma unroll
+                for (int k = 0; k < kUmmaBK / 16; ++k) {
+                  // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
+                  umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            (kb | sl | k) != 0 ? 1u : 0u);
+                }
               }
             }
           }
@@ -535,13 +570,17 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     const int ew = warp - kUmmaEpiWarp0;  // 0..15
     const int wg = ew >> 2;               // epilogue warpgroup 0..3
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-    // MT = 1: the four warpgroups split a tile's columns four ways; MT = 2: two per M tile
+    // MT = 1: the four warpgroups split the columns four ways; MT = 2: two per M tile
     const int m_tile = (MT == 2) ? (wg & 1) : 0;
     const int col_group = (MT == 2) ? (wg >> 1) : wg;
     constexpr int kColGroups = (MT == 2) ? kUmmaEpiGroups / 2 : kUmmaEpiGroups;
-    const int b = m_tile * 128 + quad * 32 + lane;
+    // the replica whose rows sit in this quadrant's lanes, and the batch row of this thread
+    const int lanes_per_replica = 128 / R;
+    const int replica = (quad * 32) / lanes_per_replica;
+    const int b = m_tile * 128 + quad * 32 + lane - replica * lanes_per_replica;
     const bool row_ok = b < p.B;
-    const bool warp_ok = (m_tile * 128 + quad * 32) < p.B;
+    const bool warp_ok = (m_tile * 128 + quad * 32 - replica * lanes_per_replica) < p.B;
+    const int cand_row = (R > 1) ? quad * 32 + lane : b;  // row of the S > 1 scratch: replicas must not share one
 
     const bool greedy = (p.flags & kFlagGreedy) != 0;
     const bool ext = (p.flags & kFlagExtNoise) != 0;
@@ -556,32 +595,35 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy, resolve_seed(p.seed, p.flags)};
     const int S = p.S;
-    const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
+    const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.cand_rows);
+    const bool narrow = (R == 4);  // four replicas leave ~50 columns per quadrant: deal them out in 16-column chunks
 
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
     float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
 
-    TileWalk walk(units_total, n_tiles, tail1, tail2);
-    const int total_tiles = walk.count();
-    for (int t = 0, ta = 0; t < total_tiles; ++t) {
+    TileWalk walk(units_total, n_tiles);
+    for (int t = 0, ta = 0; t < n_tiles; ++t) {
       const TileInfo ti = walk.next();
       const int v0 = ti.v0, NT = ti.nt;
       if (NT == 0) continue;
-      // column range of this warp inside the tile: whole 32-column chunks, dealt out evenly
-      const int chunks = (NT + 31) / 32;
-      const int per_group = (chunks + kColGroups - 1) / kColGroups;
-      const int c_begin = min(col_group * per_group * 32, NT);
-      const int c_end = min(c_begin + per_group * 32, NT);
+      // column range of this warp inside the tile: the replica's columns, dealt out to the column groups
+      int r_begin = 0, r_end = NT, c_begin, c_end;
+      if (R > 1) replica_columns(NT, R, replica, r_begin, r_end);
+      if (narrow) group_columns<16>(r_begin, r_end, col_group, kColGroups, c_begin, c_end);
+      else group_columns<32>(r_begin, r_end, col_group, kColGroups, c_begin, c_end);
       const int j = ta % acc_stages;
       const uint32_t un = (uint32_t)(ta / acc_stages);
       ++ta;
       if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
       tc_fence_after();
-      if (ew == 0 && lane == 0 && t == total_tiles - 1) stamp(p, 4);
+      if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
       if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
-        if constexpr (LSE) lse_tile_columns(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
+        if constexpr (LSE) {
+          if (narrow) lse_tile_columns<16>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
+          else lse_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
+        }
         for (int s = 0; s < S; ++s) {
           float bv = best_val;
           int bi = best_idx;
@@ -589,10 +631,11 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             bv = -INFINITY;
             bi = kIdxNone;
           }
-          scan_tile_columns(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
+          if (narrow) scan_tile_columns<16>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
+          else scan_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
           if (S > 1) {
             if (row_ok) {
-              const size_t o = slot_row + (size_t)s * p.B + b;
+              const size_t o = slot_row + (size_t)s * p.cand_rows + cand_row;
               if (bv > p.cand_val[o]) {  // later tiles have larger indices: strict compare keeps the lowest
                 p.cand_val[o] = bv;
                 p.cand_idx[o] = bi;
@@ -615,15 +658,16 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         if (best_idx != kIdxNone) atomicMax(&p.keys[b], cand_key(best_val, best_idx));
       } else {
         for (int s = 0; s < S; ++s) {
-          const size_t o = slot_row + (size_t)s * p.B + b;
+          const size_t o = slot_row + (size_t)s * p.cand_rows + cand_row;
           const int ci = p.cand_idx[o];
           if (ci != kIdxNone) atomicMax(&p.keys[(size_t)s * p.B + b], cand_key(p.cand_val[o], ci));
         }
       }
       // every tile has been multiplied, so the pipeline's first stage is free: it collects the
-      // column groups' partial sums of each row
+      // partial sums of each row, one per (replica, column group)
       if constexpr (LSE)
-        reinterpret_cast<unsigned long long*>(smem)[col_group * (MT * 128) + b] = lse_pack(lse_m, lse_l);
+        reinterpret_cast<unsigned long long*>(smem)[(replica * kColGroups + col_group) * (MT * 128) + b] =
+            lse_pack(lse_m, lse_l);
     }
   }
 
@@ -635,13 +679,12 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if constexpr (LSE) {
-    // one partial row per CTA: the column groups' sums merged in a fixed order
+    // one partial row per CTA: the (replica, column group) sums merged in a fixed order
     constexpr int kGroups = (MT == 2) ? kUmmaEpiGroups / 2 : kUmmaEpiGroups;
     const unsigned long long* part = reinterpret_cast<const unsigned long long*>(smem);
     for (int r = tid; r < MT * 128 && r < p.B; r += kUmmaThreads) {
       float m = -INFINITY, l = 0.f;
-#pragma unroll
-      for (int g = 0; g < kGroups; ++g) lse_merge_packed(m, l, part[g * (MT * 128) + r]);
+      for (int g = 0; g < kGroups * R; ++g) lse_merge_packed(m, l, part[g * (MT * 128) + r]);
       p.lse[(size_t)cta * p.B + r] = lse_pack(m, l);
     }
   }

@@ -34,6 +34,20 @@ def _tp_worker(world):
                 got = fs.fused_mm_sample(w_local, h.to(dev), S, t, seed=42, tp=tp, kernel=kernel)
                 assert torch.equal(got, full), (mode, rep, tp.rank, (got != full).sum().item())
         fs.check_status()
+    # a vocabulary that does not divide by the number of ranks: the last rank holds the remainder rows and
+    # every rank takes the global id of its first row (ids and noise keys) from the total size in TPInfo
+    V, D, B, S = 16384 + 5, 256, 33, 2
+    tpv = TPInfo.from_world(vocab_size=V)
+    w, h = gaussian_head(V, D, B, 0.08, seed=V)
+    t = (torch.rand(B, generator=torch.Generator().manual_seed(2)) + 0.5).to(dev)
+    full = fs.fused_mm_sample(w.to(dev), h.to(dev), S, t, seed=43)
+    w_local = shard_weights(w, tpv, keep_remainder=True).contiguous().to(dev)
+    assert w_local.shape[0] == tpv.shard_rows()[1] - tpv.shard_rows()[0]
+    for mode in ("p2p", "nccl"):
+        os.environ["FMMS_TP_EXCHANGE"] = mode
+        got = fs.fused_mm_sample(w_local, h.to(dev), S, t, seed=43, tp=tpv)
+        assert torch.equal(got, full), (mode, tp.rank, (got != full).sum().item())
+    fs.check_status()
     os.environ["FMMS_TP_EXCHANGE"] = "p2p"
     # a captured tensor-parallel step replays: the exchange keeps its step counter on the device
     V, D, B, S = 16384 - 16384 % world, 256, 32, 1
@@ -88,6 +102,13 @@ def test_sharded_draw_equals_unsharded_tp4():
     from flashsampling_b200.tp_info import run_maybe_distributed
 
     run_maybe_distributed(_tp_worker, 4, 4)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_sharded_draw_equals_unsharded_tp8():
+    from flashsampling_b200.tp_info import run_maybe_distributed
+
+    run_maybe_distributed(_tp_worker, 8, 8)
 
 
 def test_exchange_wait_is_bounded_and_reports_timeout():
