@@ -249,10 +249,14 @@ def run_b200(args):
         seed = [0]
         turn = [0]
 
+        # the call an engine makes: a sampler prepared once per weight (provider registry of the reference)
+        samplers = [fs.get_sampler("fused-b200", wc).prepare() for wc in ws]
+
         def step():
             seed[0] += S
             turn[0] += 1
-            return fs.fused_mm_sample(ws[turn[0] % n_copies], h, S, t, seed=seed[0], tp=tp)
+            return samplers[turn[0] % n_copies].sample(hidden_states=h, num_samples=S, temperature=t, seed=seed[0],
+                                                       tp=tp)
 
         step()
         fs.check_status()
@@ -303,17 +307,14 @@ def run_b200(args):
             pair["pair_plain_ms"], pair["pair_logprob_ms"] = both[0::2], both[1::2]
         if with_e2e:
             h_host = h.cpu().pin_memory()
-            t_host = t.cpu().pin_memory()
-            h_dev = torch.empty_like(h)
-            t_dev = torch.empty_like(t)
+            t_host = t.cpu().reshape(-1).pin_memory()
 
             def e2e_step():
+                # host buffers in, host ids out: one call of the prepared sampler (FMMS_FLAG_HOST_IO of the C
+                # ABI: H2D copies of hidden states and temperatures, the kernel, D2H copy of the ids, stream wait)
                 seed[0] += S
                 turn[0] += 1
-                h_dev.copy_(h_host, non_blocking=True)
-                t_dev.copy_(t_host, non_blocking=True)
-                ids = fs.fused_mm_sample(ws[turn[0] % n_copies], h_dev, S, t_dev, seed=seed[0], tp=tp)
-                return ids.cpu()
+                return samplers[turn[0] % n_copies].sample_host(h_host, S, t_host, seed=seed[0], tp=tp)
 
             for _ in range(max(3, warmup // 2)):
                 e2e_step()
@@ -478,7 +479,8 @@ def run_b200(args):
         "e2e": {
             "value": round(statistics.median(main["e2e_ms"]) * 1e3, 3), "unit": "us",
             "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"],
-            "note": "pinned host hidden states + temperature -> device, sample, ids -> host; wall clock per step",
+            "note": "PreparedSampler.sample_host: pinned host hidden states + temperature -> device, sample, ids -> host, "
+                    "stream wait, all inside one C-ABI call (fmms_run with FMMS_FLAG_HOST_IO); wall clock per step",
         },
         "roofline": ({
             "bound": "tensor", "achieved": round(flops / (mean_ms * 1e-3) / 1e12, 1), "peak": tflops_peak,

@@ -2,6 +2,7 @@
 
 from .core import (  # noqa: F401
     PROVIDERS,
+    PreparedSampler,
     Sampler,
     SimpleSampler,
     check_status,

@@ -17,7 +17,48 @@ OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH
 FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA, FLAG_TWO_STAGE = 1, 2, 4, 8, 16, 32
 FLAG_SEED_DEVICE = 64
 FLAG_LOGPROB = 128
+FLAG_HOST_IO = 256
+FLAG_NO_SYNC = 512
 PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
+
+class FmmsCall(ctypes.Structure):
+    """``fmms_call_t`` of include/fmms_b200.h, field for field."""
+
+    _fields_ = [
+        ("struct_bytes", c_size_t),
+        ("W_bf16", c_void_p),
+        ("H_bf16", c_void_p),
+        ("temperature", c_void_p),
+        ("temp_stride", c_int),
+        ("V_local", c_int),
+        ("D", c_int),
+        ("B", c_int),
+        ("S", c_int),
+        ("seed", c_ulonglong),
+        ("v_global_offset", c_longlong),
+        ("flags", c_int),
+        ("ext_noise", c_void_p),
+        ("noise_ld", c_longlong),
+        ("logits_out", c_void_p),
+        ("out_idx", c_void_p),
+        ("out_val", c_void_p),
+        ("out_logprob", c_void_p),
+        ("out_lse", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+        ("status_dev", c_void_p),
+        ("stream", c_void_p),
+        ("tp_rank", c_int),
+        ("tp_world", c_int),
+        ("tp_max_items", c_int),
+        ("tp_peer_buffers", ctypes.POINTER(c_void_p)),
+        ("tp_epoch", ctypes.c_uint),
+        ("tp_wait_limit_ns", c_ulonglong),
+        ("staging", c_void_p),
+        ("staging_bytes", c_size_t),
+        ("status_host", c_void_p),
+    ]
+
 
 # every symbol the header declares: name -> (restype, argtypes)
 SIGNATURES = {
@@ -66,6 +107,8 @@ SIGNATURES = {
             c_void_p, c_void_p,  # out_logprob, out_lse
         ],
     ),
+    "fmms_run": (c_int, [ctypes.POINTER(FmmsCall)]),
+    "fmms_query_staging": (c_int, [c_int, c_int, c_int, ctypes.POINTER(c_size_t)]),
     "fmms_last_path": (c_int, []),
     "fmms_l2_sweep": (c_int, [c_void_p, c_size_t, c_void_p]),
     "fmms_debug_stamps": (c_int, [c_void_p]),
@@ -134,6 +177,12 @@ def check(status: int, where: str) -> None:
 def query_workspace(v_local: int, d: int, b: int, s: int) -> int:
     n = c_size_t(0)
     check(load().fmms_query_workspace(v_local, d, b, s, ctypes.byref(n)), "fmms_query_workspace")
+    return int(n.value)
+
+
+def query_staging(d: int, b: int, s: int) -> int:
+    n = c_size_t(0)
+    check(load().fmms_query_staging(d, b, s, ctypes.byref(n)), "fmms_query_staging")
     return int(n.value)
 
 

@@ -13,6 +13,7 @@ no CPU path: without the CUDA library or a GPU the call raises.
 from __future__ import annotations
 
 import contextlib
+import ctypes
 from dataclasses import dataclass
 from typing import Callable, Protocol
 
@@ -27,6 +28,7 @@ __all__ = [
     "get_sampler",
     "Sampler",
     "SimpleSampler",
+    "PreparedSampler",
     "check_status",
     "last_path",
     "PROVIDERS",
@@ -34,6 +36,7 @@ __all__ = [
 
 _nullcontext = contextlib.nullcontext()
 _workspaces: dict[tuple, torch.Tensor] = {}
+_all_workspaces: list[torch.Tensor] = []  # also those a larger one replaced (prepared calls may still use them)
 _ws_bytes: dict[tuple, int] = {}  # (B, S) -> workspace bytes (independent of V and D)
 _status: dict[int, torch.Tensor] = {}
 
@@ -43,8 +46,9 @@ def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tenso
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         # zeroed once: the kernels keep the head of the workspace (packed winners, CTA counter) at zero
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
+        _all_workspaces.append(ws)
     return ws
 
 
@@ -70,8 +74,8 @@ def check_status(device: torch.device | None = None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
-            for key, ws in _workspaces.items():
-                if key[0] == idx:
+            for ws in _all_workspaces:
+                if ws.device.index == idx:
                     ws.zero_()  # an aborted kernel may have left candidates behind
             raise _lib.FmmsError(code, "fused_mm_sample (device status word)")
 
@@ -257,15 +261,203 @@ class Sampler(Protocol):
 
 @dataclass
 class SimpleSampler:
-    """core.py:666-674."""
+    """core.py:666-674.  ``prepare()`` binds the sampler to its weight matrix (``PreparedSampler``)
+    when one was given to ``get_sampler``."""
 
     fn: Callable[..., torch.Tensor]
+    weights: torch.Tensor | None = None
+    defaults: dict | None = None
 
-    def prepare(self) -> "SimpleSampler":
+    def prepare(self) -> "Sampler":
+        if self.weights is not None and self.weights.is_cuda:
+            return PreparedSampler(self.weights, self.fn, dict(self.defaults or {}))
         return self
 
     def sample(self, **kwargs) -> torch.Tensor:
         return self.fn(**kwargs)
+
+
+def _raw_stream(dev_index: int) -> int:
+    return torch._C._cuda_getCurrentRawStream(dev_index)
+
+
+class _PreparedCall:
+    """One call descriptor (``fmms_call_t``) with everything filled in that stays the same from step
+    to step; ``sample`` only rewrites the hidden-state, temperature, seed and output fields."""
+
+    __slots__ = ("c", "ref", "keep")
+
+    def __init__(self, c: "_lib.FmmsCall", keep: tuple):
+        self.c = c
+        self.ref = ctypes.byref(c)
+        self.keep = keep  # tensors and ctypes arrays the descriptor points into
+
+
+class PreparedSampler:
+    """A sampler bound to one LM-head weight (``get_sampler(provider, weights).prepare()``).
+
+    The decode loop of an engine calls ``sample`` with the same weight, batch shape and dtype on
+    every step.  Everything that does not change is therefore resolved once per (batch rows, draws,
+    temperature layout, tensor-parallel group, stream): argument checks, the scratch workspace, the
+    status word, the vocabulary offset of a shard, the exchange buffers, and the C call descriptor,
+    which is updated in place.  A call that does not fit this pattern (noise, logits or
+    log-probabilities requested, a tensor seed, another weight ...) takes the general
+    ``fused_mm_sample`` path with the same results.
+
+    ``sample_host`` is the same step for hidden states that arrive in HOST memory: one library call
+    copies them in, samples and copies the ids out (``FMMS_FLAG_HOST_IO`` of the C ABI).
+    """
+
+    _FAST_KEYS = frozenset(("weights", "hidden_states", "num_samples", "temperature", "seed", "tp"))
+
+    def __init__(self, weights: torch.Tensor, fn: Callable[..., torch.Tensor], defaults: dict):
+        if not weights.is_cuda or weights.ndim != 2 or weights.dtype != torch.bfloat16 or not weights.is_contiguous():
+            raise ValueError("weights must be a contiguous [V, D] bfloat16 CUDA tensor")
+        self.weights = weights
+        self.fn = fn
+        self.defaults = defaults
+        self.V, self.D = weights.shape
+        self.dev = weights.device
+        self.dev_index = weights.device.index if weights.device.index is not None else torch.cuda.current_device()
+        self.lib = _lib.load()
+        self.run = self.lib.fmms_run
+        self.w_ptr = weights.data_ptr()
+        # defaults that the fast path cannot honour send every call down the general path
+        self.fast_ok = not any(defaults.get(k) for k in ("return_logits", "greedy_sampling"))
+        self.seed_default = int(defaults.get("seed", 0))
+        self._calls: dict[tuple, _PreparedCall] = {}
+        self._host_calls: dict[tuple, tuple] = {}
+
+    def prepare(self) -> "PreparedSampler":
+        return self
+
+    # ---- device tensors in, device tensor out ---------------------------------------------
+    def sample(self, **kw) -> torch.Tensor:
+        if self.fast_ok and self._FAST_KEYS.issuperset(kw):
+            w = kw.get("weights")
+            hs = kw.get("hidden_states")
+            t = kw.get("temperature")
+            seed = kw.get("seed", self.seed_default)
+            if (
+                (w is None or w is self.weights or (w.data_ptr() == self.w_ptr and w.shape == self.weights.shape))
+                and type(hs) is torch.Tensor and type(t) is torch.Tensor and type(seed) is int
+                and hs.dtype is torch.bfloat16 and t.dtype is torch.float32
+                and hs.ndim == 2 and hs.shape[1] == self.D and hs.is_contiguous()
+                and hs.device == self.dev and t.device == self.dev
+                and torch._C._cuda_getDevice() == self.dev_index
+            ):
+                B = hs.shape[0]
+                nt = t.numel()
+                S = kw["num_samples"]
+                tp = kw.get("tp", TP1)
+                if (nt == 1 or (nt == B and t.is_contiguous())) and S >= 1 and 0 < B <= 256:
+                    stream = _raw_stream(self.dev_index)
+                    key = (B, S, nt != 1, tp, stream)
+                    call = self._calls.get(key)
+                    if call is None:
+                        call = self._make_call(B, S, 1 if nt != 1 else 0, tp, stream)
+                    if call is not False:
+                        out = torch.empty((B, S), dtype=torch.int64, device=self.dev)
+                        c = call.c
+                        c.H_bf16 = hs.data_ptr()
+                        c.temperature = t.data_ptr()
+                        c.seed = seed & 0xFFFFFFFFFFFFFFFF
+                        c.out_idx = out.data_ptr()
+                        rc = self.run(call.ref)
+                        if rc:
+                            raise _lib.FmmsError(rc, "fmms_run")
+                        return out
+        return self.fn(**kw)
+
+    def _make_call(self, B: int, S: int, temp_stride: int, tp: TPInfo, stream: int, host: bool = False):
+        """Resolve the step-invariant part of a call; ``False`` marks a shape the fast path leaves to
+        the general one (a tensor-parallel call that cannot use the fused exchange)."""
+        c = _lib.FmmsCall()
+        c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
+        c.W_bf16 = self.w_ptr
+        c.temp_stride = temp_stride
+        c.V_local, c.D, c.B, c.S = self.V, self.D, B, S
+        c.flags = 0
+        keep: list = []
+        if tp.size > 1:
+            from .tensor_parallel import get_exchange
+
+            exchange = get_exchange(tp, self.dev)
+            if not (getattr(exchange, "fused", False) and B * S <= exchange.max_items):
+                if not host:
+                    self._calls[(B, S, bool(temp_stride), tp, stream)] = False
+                return False
+            c.v_global_offset = exchange.vocab_offset(self.V, tp)
+            c.tp_rank, c.tp_world, c.tp_max_items = tp.rank, tp.size, exchange.max_items
+            c.tp_peer_buffers = exchange.ptrs
+            c.tp_epoch = exchange.next_epoch()
+            keep.append(exchange)
+        nbytes = _ws_bytes.get((B, S))
+        if nbytes is None:
+            nbytes = _ws_bytes[(B, S)] = _lib.query_workspace(self.V, self.D, B, S)
+        ws = _workspace(self.dev, stream, nbytes)
+        status = _status_word(self.dev)
+        c.workspace, c.workspace_bytes = ws.data_ptr(), ws.numel()
+        c.status_dev = status.data_ptr()
+        c.stream = stream
+        keep += [ws, status, self.weights]
+        call = _PreparedCall(c, tuple(keep))
+        if not host:
+            self._calls[(B, S, bool(temp_stride), tp, stream)] = call
+        return call
+
+    # ---- host tensors in, host tensor out ---------------------------------------------------
+    def sample_host(self, hidden_states: torch.Tensor, num_samples: int, temperature: torch.Tensor,
+                    seed: int = 0, tp: TPInfo = TP1) -> torch.Tensor:
+        """The step for hidden states ``[B, D]`` (bf16) and temperature(s) (fp32, one or one per
+        row) in host memory - pinned memory avoids a staging copy by the driver.  One library call
+        enqueues the copies to the device, the sampling kernel and the copy of the ids back, and
+        waits for the stream.  Returns an int64 ``[B, num_samples]`` CPU tensor and raises if the
+        kernel reported a device-side time-out.  Same ids as ``sample`` for the same seed."""
+        if hidden_states.is_cuda or temperature.is_cuda:
+            raise ValueError("sample_host takes CPU tensors; use sample() for CUDA tensors")
+        if hidden_states.dtype != torch.bfloat16 or hidden_states.ndim != 2 or hidden_states.shape[1] != self.D:
+            raise ValueError(f"hidden_states must be bfloat16 [B, {self.D}]")
+        if temperature.dtype != torch.float32:
+            raise TypeError("temperature must be float32")
+        hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
+        B = hs.shape[0]
+        nt = temperature.numel()
+        if nt != 1 and nt != B:
+            raise ValueError(f"temperature must have 1 or {B} elements, got {nt}")
+        if not 0 < B <= 256:
+            raise ValueError("sample_host handles 1..256 rows per call")
+        with (_nullcontext if torch._C._cuda_getDevice() == self.dev_index else torch.cuda.device(self.dev)):
+            stream = _raw_stream(self.dev_index)
+            key = (B, num_samples, nt != 1, tp, stream)
+            entry = self._host_calls.get(key)
+            if entry is None:
+                call = self._make_call(B, num_samples, 1 if nt != 1 else 0, tp, stream, host=True)
+                if call is False:
+                    raise ValueError("this tensor-parallel call does not fit the fused exchange")
+                staging = torch.empty(_lib.query_staging(self.D, B, num_samples), dtype=torch.uint8, device=self.dev)
+                out_host = torch.empty((B, num_samples), dtype=torch.int64).pin_memory()
+                status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+                call.c.flags |= _lib.FLAG_HOST_IO
+                call.c.staging, call.c.staging_bytes = staging.data_ptr(), staging.numel()
+                call.c.out_idx = out_host.data_ptr()
+                call.c.status_host = status_host.data_ptr()
+                call.keep += (staging, out_host, status_host)
+                entry = self._host_calls[key] = (call, out_host, status_host)
+            call, out_host, status_host = entry
+            c = call.c
+            c.H_bf16 = hs.data_ptr()
+            c.temperature = temperature.data_ptr()
+            c.seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+            rc = self.run(call.ref)
+        if rc:
+            raise _lib.FmmsError(rc, "fmms_run (host buffers)")
+        code = int(status_host[0])
+        if code:
+            status_host.zero_()
+            check_status(self.dev)  # clears the device word and the workspace, raises
+            raise _lib.FmmsError(code, "fmms_run (device status word)")
+        return out_host.clone()
 
 
 PROVIDERS = (
@@ -286,11 +478,14 @@ def get_sampler(provider: str, weights: torch.Tensor) -> Sampler:
     this library and raises ``NotImplementedError``.
     """
     if provider in ("fused-b200", "fused-triton"):
-        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, **kw}))
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, **kw}), weights, {"seed": 0})
     if provider == "fused-triton-p2p-no-overlap":
-        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "p2p_no_overlap": True, **kw}))
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "p2p_no_overlap": True, **kw}), weights,
+                             {"seed": 0})
     if provider == "fused-triton-ret-logits":
-        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "return_logits": True, **kw})[0])
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "return_logits": True, **kw})[0], weights,
+                             {"seed": 0, "return_logits": True})
     if provider == "fused-triton-greedy":
-        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "greedy_sampling": True, **kw}))
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "greedy_sampling": True, **kw}), weights,
+                             {"seed": 0, "greedy_sampling": True})
     raise NotImplementedError(f"Unknown provider: {provider} (this library implements {PROVIDERS})")

@@ -90,20 +90,36 @@ struct MapEntry {
   MapKey key;
   CUtensorMap map;
 };
-static std::vector<MapEntry> g_maps;
+// Two caches: descriptors of weight matrices (few, long-lived) and of hidden-state matrices.  A
+// serving engine may hand over a fresh hidden-state tensor every step: those misses cost one
+// host-side encode each and must never evict a weight descriptor.
+struct MapCache {
+  std::vector<MapEntry> entries;
+  size_t capacity;
+};
+static MapCache g_maps_w{{}, 64}, g_maps_h{{}, 16};
+
+static bool map_cache_find(MapCache& c, const MapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (const MapEntry& e : c.entries)
+    if (e.key == key) {
+      *out = e.map;
+      return true;
+    }
+  return false;
+}
+static void map_cache_put(MapCache& c, const MapKey& key, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (c.entries.size() >= c.capacity) c.entries.erase(c.entries.begin());
+  c.entries.push_back(MapEntry{key, m});
+}
 
 // Row-major [rows, cols] bf16 matrix, box = box_rows x box_cols, out-of-range elements read as zero.
 static int get_tensor_map(const void* ptr, long long rows, long long cols, int box_rows, int box_cols,
-                          CUtensorMapSwizzle swz, CUtensorMap* out) {
-  MapKey key{ptr, rows, cols, box_rows, box_cols, (int)swz};
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    for (const MapEntry& e : g_maps)
-      if (e.key == key) {
-        *out = e.map;
-        return kOk;
-      }
-  }
+                          CUtensorMapSwizzle swz, CUtensorMap* out, bool hidden = false) {
+  MapCache& cache = hidden ? g_maps_h : g_maps_w;
+  const MapKey key{ptr, rows, cols, box_rows, box_cols, (int)swz};
+  if (map_cache_find(cache, key, out)) return kOk;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return kErrCuda;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -115,11 +131,7 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, int b
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return kErrCuda;
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (g_maps.size() >= 64) g_maps.erase(g_maps.begin());
-    g_maps.push_back(MapEntry{key, m});
-  }
+  map_cache_put(cache, key, m);
   *out = m;
   return kOk;
 }
@@ -145,16 +157,10 @@ static size_t workspace_item_capacity(size_t bytes) {
 
 // [rows, cols] bf16 matrix seen as (inner columns, rows, cols / inner groups); box = inner x box_rows x groups.
 static int get_tensor_map_3d(const void* ptr, long long rows, long long cols, int inner, int box_rows, int slabs,
-                             CUtensorMapSwizzle swz, CUtensorMap* out) {
-  MapKey key{ptr, rows, cols, box_rows, inner + 1000 * slabs, (int)swz};
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    for (const MapEntry& e : g_maps)
-      if (e.key == key) {
-        *out = e.map;
-        return kOk;
-      }
-  }
+                             CUtensorMapSwizzle swz, CUtensorMap* out, bool hidden = false) {
+  MapCache& cache = hidden ? g_maps_h : g_maps_w;
+  const MapKey key{ptr, rows, cols, box_rows, inner + 1000 * slabs, (int)swz};
+  if (map_cache_find(cache, key, out)) return kOk;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return kErrCuda;
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(cols / inner)};
@@ -166,17 +172,13 @@ static int get_tensor_map_3d(const void* ptr, long long rows, long long cols, in
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return kErrCuda;
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (g_maps.size() >= 64) g_maps.erase(g_maps.begin());
-    g_maps.push_back(MapEntry{key, m});
-  }
+  map_cache_put(cache, key, m);
   *out = m;
   return kOk;
 }
 static int get_tensor_map_slabs(const void* ptr, long long rows, long long cols, int box_rows, int slabs,
-                                CUtensorMap* out) {
-  return get_tensor_map_3d(ptr, rows, cols, 64, box_rows, slabs, CU_TENSOR_MAP_SWIZZLE_128B, out);
+                                CUtensorMap* out, bool hidden = false) {
+  return get_tensor_map_3d(ptr, rows, cols, 64, box_rows, slabs, CU_TENSOR_MAP_SWIZZLE_128B, out, hidden);
 }
 static int get_tensor_map_chunks(const void* ptr, long long rows, long long cols, int box_rows, int chunks,
                                  CUtensorMap* out) {
@@ -330,7 +332,7 @@ static int build_umma_maps(const void* W, const void* H, const SampleParams& p, 
       rc = get_tensor_map_slabs(W, p.V, p.D, (pl.q_units - 1) * 16, pl.slabs, &mp->wq1);
       if (rc != kOk) return rc;
     }
-    rc = get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.slabs, &mp->hm);
+    rc = get_tensor_map_slabs(H, p.B, p.D, pl.h_rows, pl.slabs, &mp->hm, /*hidden=*/true);
     if (rc != kOk) return rc;
   } else {
     rc = get_tensor_map(W, p.V, p.D, pl.q_units * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->wq);
@@ -340,7 +342,7 @@ static int build_umma_maps(const void* W, const void* H, const SampleParams& p, 
       rc = get_tensor_map(W, p.V, p.D, (pl.q_units - 1) * 16, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->wq1);
       if (rc != kOk) return rc;
     }
-    rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->hm);
+    rc = get_tensor_map(H, p.B, p.D, pl.h_rows, kUmmaBK, CU_TENSOR_MAP_SWIZZLE_128B, &mp->hm, /*hidden=*/true);
     if (rc != kOk) return rc;
   }
   return kOk;
@@ -400,7 +402,7 @@ static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleP
     rc = get_tensor_map_slabs(W, p.V, p.D, (pl.q_units - 1) * 16, pl.slabs, &wq1);
     if (rc != kOk) return -rc;
   }
-  rc = get_tensor_map_slabs(H, p.B, p.D, 128, pl.slabs, &hm);
+  rc = get_tensor_map_slabs(H, p.B, p.D, 128, pl.slabs, &hm, /*hidden=*/true);
   if (rc != kOk) return -rc;
   const bool lse = (p.flags & kFlagLogprob) != 0;
   if (!d.umma_attr[lse][3]) {
@@ -562,7 +564,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
                        size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
-                       float* out_logprob, float* out_lse);
+                       float* out_logprob, float* out_lse, int* status_mirror);
 
 struct TpArgs {
   int rank, world, max_items;
@@ -576,7 +578,7 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, float* logits_out,
                        long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
                        int* status_dev, void* stream_v, const TpArgs* tpa, float* out_logprob = nullptr,
-                       float* out_lse = nullptr) {
+                       float* out_lse = nullptr, int* status_mirror = nullptr) {
   g_last_path = FMMS_PATH_NONE;
   if (!W_bf16 || !H_bf16 || !out_idx || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
   const bool greedy = flags & FMMS_FLAG_GREEDY, ext = flags & FMMS_FLAG_EXT_NOISE;
@@ -606,14 +608,14 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                                  out_idx + (size_t)b0 * S, out_val ? out_val + (size_t)b0 * S : nullptr, workspace,
                                  workspace_bytes, status_dev, stream_v, nullptr,
                                  out_logprob ? out_logprob + (size_t)b0 * S : nullptr,
-                                 out_lse ? out_lse + b0 : nullptr);
+                                 out_lse ? out_lse + b0 : nullptr, status_mirror);
       if (rc != FMMS_OK) return rc;
     }
     return FMMS_OK;
   }
   return sample_rows(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
                      ext_noise, noise_ld, (long long)B * noise_ld, 0, logits_out, out_idx, out_val, workspace,
-                     workspace_bytes, status_dev, stream_v, tpa, out_logprob, out_lse);
+                     workspace_bytes, status_dev, stream_v, tpa, out_logprob, out_lse, status_mirror);
 }
 
 static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
@@ -621,7 +623,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
                        size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
-                       float* out_logprob, float* out_lse) {
+                       float* out_logprob, float* out_lse, int* status_mirror) {
   const bool greedy = flags & FMMS_FLAG_GREEDY;
   (void)greedy;
   const size_t need = workspace_bytes_for(B, S);  // the least that works; fmms_query_workspace may ask for more
@@ -680,6 +682,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
     if (v_global_offset + (long long)V_local > 0xffffffffll) return FMMS_ERR_UNSUPPORTED;  // ids travel as 32 bits
   }
   p.status_dev = status_dev;
+  p.status_mirror = status_mirror;
   p.stamps = g_stamps;
 
   const bool can_gemv = gemv_eligible(*d, D, B, S);
@@ -744,6 +747,128 @@ int fmms_sample_logprobs(const void* W_bf16, const void* H_bf16, const float* te
   return sample_impl(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset,
                      flags | FMMS_FLAG_LOGPROB, ext_noise, noise_ld, logits_out, out_idx, out_val, workspace,
                      workspace_bytes, status_dev, stream, nullptr, out_logprob, out_lse);
+}
+
+// ---- one descriptor for every variant; host-memory inputs and outputs --------------------
+static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+struct StagingLayout {
+  size_t h, t, idx, val, lp, lse, total;
+};
+static StagingLayout staging_layout(int D, int B, int S) {
+  StagingLayout l{};
+  size_t off = 0;
+  l.h = off;   off += align256((size_t)B * D * 2);
+  l.t = off;   off += align256((size_t)B * 4);
+  l.idx = off; off += align256((size_t)B * S * 8);
+  l.val = off; off += align256((size_t)B * S * 4);
+  l.lp = off;  off += align256((size_t)B * S * 4);
+  l.lse = off; off += align256((size_t)B * 4);
+  l.total = off;
+  return l;
+}
+
+int fmms_query_staging(int D, int B, int S, size_t* bytes) {
+  if (!bytes || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
+  *bytes = staging_layout(D, B, S).total;
+  return FMMS_OK;
+}
+
+// Device-visible address of a host pointer (pinned or registered memory under unified addressing),
+// or null for pageable memory.  Asked afresh on every call: an address that was pinned memory once
+// may be pageable memory later.
+static void* host_ptr_on_device(const void* host) {
+  if (!host) return nullptr;
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, host) == cudaSuccess && a.type == cudaMemoryTypeHost) return a.devicePointer;
+  cudaGetLastError();  // pageable memory is not an error here
+  return nullptr;
+}
+
+// Hidden states and temperatures from device-visible host memory into the staging buffer: one small
+// kernel in place of two copy-engine operations (each of which costs a hand-over between the copy
+// and the compute engine, several microseconds, before the sampling kernel may start).
+__global__ void stage_host_inputs_kernel(const uint4* __restrict__ h_src, uint4* __restrict__ h_dst, size_t n16,
+                                         const float* __restrict__ t_src, float* __restrict__ t_dst, int nt) {
+  const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = i0; i < n16; i += stride) h_dst[i] = h_src[i];
+  for (size_t i = i0; i < (size_t)nt; i += stride) t_dst[i] = t_src[i];
+}
+
+int fmms_run(const fmms_call_t* c) {
+  if (!c || c->struct_bytes != sizeof(fmms_call_t)) return FMMS_ERR_BAD_ARG;
+  const int kernel_flags = c->flags & ~(FMMS_FLAG_HOST_IO | FMMS_FLAG_NO_SYNC);
+  TpArgs tpa{c->tp_rank, c->tp_world, c->tp_max_items, c->tp_peer_buffers, c->tp_epoch, c->tp_wait_limit_ns};
+  const TpArgs* tp = c->tp_world > 1 ? &tpa : nullptr;
+  if (!(c->flags & FMMS_FLAG_HOST_IO))
+    return sample_impl(c->W_bf16, c->H_bf16, c->temperature, c->temp_stride, c->V_local, c->D, c->B, c->S, c->seed,
+                       c->v_global_offset, kernel_flags, c->ext_noise, c->noise_ld, c->logits_out, c->out_idx,
+                       c->out_val, c->workspace, c->workspace_bytes, c->status_dev, c->stream, tp, c->out_logprob,
+                       c->out_lse);
+  // host-memory hidden states, temperatures and results
+  if (!c->H_bf16 || !c->out_idx || c->D <= 0 || c->B <= 0 || c->S <= 0 || c->D % 8 != 0) return FMMS_ERR_BAD_ARG;
+  const StagingLayout l = staging_layout(c->D, c->B, c->S);
+  if (!c->staging || c->staging_bytes < l.total || ((uintptr_t)c->staging & 255)) return FMMS_ERR_WORKSPACE;
+  if ((c->flags & FMMS_FLAG_LOGPROB) && !c->out_logprob) return FMMS_ERR_BAD_ARG;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(c->stream);
+  unsigned char* st = reinterpret_cast<unsigned char*>(c->staging);
+  const size_t n_items = (size_t)c->B * c->S;
+  const size_t h_bytes = (size_t)c->B * c->D * 2;
+  const int nt = c->temperature ? (c->temp_stride ? c->B : 1) : 0;
+
+  // Inputs.  Device-visible (pinned) host memory, 16-byte aligned: one gather kernel; else copies.
+  void* h_map = host_ptr_on_device(c->H_bf16);
+  void* t_map = nt ? host_ptr_on_device(c->temperature) : nullptr;
+  const float* temp_dev = nt ? reinterpret_cast<const float*>(st + l.t) : nullptr;
+  if (h_map && (!nt || t_map) && !((uintptr_t)h_map & 15)) {
+    const size_t n16 = h_bytes / 16;
+    int blocks = (int)((n16 + 255) / 256);
+    if (blocks > 296) blocks = 296;
+    if (blocks < 1) blocks = 1;
+    stage_host_inputs_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(h_map),
+                                                         reinterpret_cast<uint4*>(st + l.h), n16,
+                                                         reinterpret_cast<const float*>(t_map),
+                                                         reinterpret_cast<float*>(st + l.t), nt);
+    if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+  } else {
+    if (cudaMemcpyAsync(st + l.h, c->H_bf16, h_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return FMMS_ERR_CUDA;
+    if (nt && cudaMemcpyAsync(st + l.t, c->temperature, (size_t)nt * 4, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+      return FMMS_ERR_CUDA;
+  }
+
+  // Outputs.  Into device-visible host memory the kernel's last CTA writes directly (a few hundred
+  // bytes over the bus, no copy operation behind the kernel); pageable memory goes through staging.
+  long long* idx_map = reinterpret_cast<long long*>(host_ptr_on_device(c->out_idx));
+  float* val_map = c->out_val ? reinterpret_cast<float*>(host_ptr_on_device(c->out_val)) : nullptr;
+  float* lp_map = c->out_logprob ? reinterpret_cast<float*>(host_ptr_on_device(c->out_logprob)) : nullptr;
+  float* lse_map = c->out_lse ? reinterpret_cast<float*>(host_ptr_on_device(c->out_lse)) : nullptr;
+  int* status_map = (c->status_host && c->status_dev) ? reinterpret_cast<int*>(host_ptr_on_device(c->status_host)) : nullptr;
+  const bool direct = idx_map && (!c->out_val || val_map) && (!c->out_logprob || lp_map) && (!c->out_lse || lse_map) &&
+                      (!(c->status_host && c->status_dev) || status_map);
+  int rc;
+  if (direct) {
+    rc = sample_impl(c->W_bf16, st + l.h, temp_dev, c->temp_stride, c->V_local, c->D, c->B, c->S, c->seed,
+                     c->v_global_offset, kernel_flags, c->ext_noise, c->noise_ld, c->logits_out, idx_map, val_map,
+                     c->workspace, c->workspace_bytes, c->status_dev, c->stream, tp, lp_map, lse_map, status_map);
+    if (rc != FMMS_OK) return rc;
+  } else {
+    rc = sample_impl(c->W_bf16, st + l.h, temp_dev, c->temp_stride, c->V_local, c->D, c->B, c->S, c->seed,
+                     c->v_global_offset, kernel_flags, c->ext_noise, c->noise_ld, c->logits_out,
+                     reinterpret_cast<long long*>(st + l.idx),
+                     c->out_val ? reinterpret_cast<float*>(st + l.val) : nullptr, c->workspace, c->workspace_bytes,
+                     c->status_dev, c->stream, tp, c->out_logprob ? reinterpret_cast<float*>(st + l.lp) : nullptr,
+                     c->out_lse ? reinterpret_cast<float*>(st + l.lse) : nullptr);
+    if (rc != FMMS_OK) return rc;
+    bool ok = cudaMemcpyAsync(c->out_idx, st + l.idx, n_items * 8, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (c->out_val) ok = ok && cudaMemcpyAsync(c->out_val, st + l.val, n_items * 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (c->out_logprob) ok = ok && cudaMemcpyAsync(c->out_logprob, st + l.lp, n_items * 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (c->out_lse) ok = ok && cudaMemcpyAsync(c->out_lse, st + l.lse, (size_t)c->B * 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (c->status_host && c->status_dev)
+      ok = ok && cudaMemcpyAsync(c->status_host, c->status_dev, 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (!ok) return FMMS_ERR_CUDA;
+  }
+  if (!(c->flags & FMMS_FLAG_NO_SYNC) && cudaStreamSynchronize(stream) != cudaSuccess) return FMMS_ERR_CUDA;
+  return FMMS_OK;
 }
 
 // ---- tensor-parallel exchange -----------------------------------------------------------

@@ -64,6 +64,7 @@ struct SampleParams {
   float* out_logprob;        // [B, S] ln p(sampled id)
   float* out_lse;            // [B] ln sum_v exp(logit_v / T), or null
   int* status_dev;
+  int* status_mirror;        // optional: host-mapped copy of *status_dev, written by the last CTA when it is done
   unsigned long long* stamps;  // optional [gridDim.x][8] %globaltimer stamps of the kernel's phases (null = off)
   int stages;                // shared-memory ring depth
   int gemv_chunks;           // weight-streaming kernel: 256-column chunks fetched per TMA operation
@@ -179,6 +180,8 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
       *p.ticket = 0u;
       *p.sched = 0u;
       stamp(p, 7);
+      // every other CTA has finished its waits before this one took the last ticket
+      if (p.status_mirror && p.status_dev) *p.status_mirror = *reinterpret_cast<volatile int*>(p.status_dev);
     }
     return;
   }
@@ -218,6 +221,10 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
     if (p.out_val) p.out_val[(size_t)b * p.S + s] = bv;
   }
   if (tid == 0) stamp(p, 7);
+  if (p.status_mirror && p.status_dev) {
+    sync();  // the receive loop above may have recorded a time-out
+    if (tid == 0) *p.status_mirror = *reinterpret_cast<volatile int*>(p.status_dev);
+  }
 }
 
 __host__ __device__ inline int gemv_dpad(int D, int chunks) {

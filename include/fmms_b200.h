@@ -52,6 +52,11 @@ extern "C" {
 #define FMMS_FLAG_LOGPROB 128      /* set by fmms_sample_logprobs(): the pass also accumulates each
                                       row's log-sum-exp and reports ln p(sampled id)            */
 
+#define FMMS_FLAG_HOST_IO 256      /* fmms_run() only: H_bf16, temperature and the outputs out_idx / out_val /
+                                      out_logprob / out_lse are HOST pointers (pinned memory recommended); the
+                                      call copies them through the caller's device `staging` buffer           */
+#define FMMS_FLAG_NO_SYNC 512      /* with FMMS_FLAG_HOST_IO: do not wait for the stream before returning   */
+
 /* kernel paths reported by fmms_last_path() */
 #define FMMS_PATH_NONE 0
 #define FMMS_PATH_GEMV 1
@@ -180,6 +185,61 @@ int fmms_sample_logprobs(const void* W_bf16, const void* H_bf16, const float* te
                          float* logits_out, long long* out_idx, float* out_val, void* workspace,
                          size_t workspace_bytes, int* status_dev, void* stream, float* out_logprob,
                          float* out_lse);
+
+/*
+ * One call descriptor for every variant of the sampling step: fmms_run(&call) is fmms_sample(),
+ * fmms_sample_tp() (tp_world > 1) or fmms_sample_logprobs() (FMMS_FLAG_LOGPROB) with the
+ * arguments taken from the structure, which a host keeps and updates in place between steps
+ * (only H_bf16, temperature, seed and the output pointers change from step to step).  Set
+ * `struct_bytes = sizeof(fmms_call_t)`; fields a call does not use are zero.
+ *
+ * With FMMS_FLAG_HOST_IO the hidden states, the temperatures and the results live in HOST
+ * memory: the call enqueues the host-to-device copies into `staging` (device memory of at
+ * least fmms_query_staging() bytes, 256-byte aligned), the sampling kernel, and the
+ * device-to-host copies of the ids (and of out_val / out_logprob / out_lse when given, and of
+ * the status word into `status_host` when given), then waits for the stream unless
+ * FMMS_FLAG_NO_SYNC is set.  W_bf16, ext_noise, logits_out, workspace and status_dev stay device
+ * pointers.  This is the whole decode-side hand-over of an engine whose hidden states arrive in
+ * host memory, in one library call.  The reference has no counterpart (its entry point takes
+ * CUDA tensors, core.py:224-235).
+ */
+typedef struct fmms_call {
+  size_t struct_bytes;
+  const void* W_bf16;
+  const void* H_bf16;
+  const float* temperature;
+  int temp_stride;
+  int V_local, D, B, S;
+  unsigned long long seed;
+  long long v_global_offset;
+  int flags;
+  const float* ext_noise;
+  long long noise_ld;
+  float* logits_out;
+  long long* out_idx;
+  float* out_val;
+  float* out_logprob; /* FMMS_FLAG_LOGPROB */
+  float* out_lse;     /* FMMS_FLAG_LOGPROB, nullable */
+  void* workspace;
+  size_t workspace_bytes;
+  int* status_dev;
+  void* stream;
+  /* tensor parallelism: tp_world > 1 selects the fused exchange of fmms_sample_tp() */
+  int tp_rank, tp_world, tp_max_items;
+  void* const* tp_peer_buffers;
+  unsigned int tp_epoch;
+  unsigned long long tp_wait_limit_ns;
+  /* FMMS_FLAG_HOST_IO */
+  void* staging;
+  size_t staging_bytes;
+  int* status_host;
+} fmms_call_t;
+
+int fmms_run(const fmms_call_t* call);
+
+/* Bytes of device staging that fmms_run() needs with FMMS_FLAG_HOST_IO for B rows of D hidden
+ * values and S draws. No reference counterpart. */
+int fmms_query_staging(int D, int B, int S, size_t* bytes);
 
 /* Size of one rank's symmetric buffer for `world` ranks and up to `max_items` (B * S)
  * items per step. */
