@@ -215,10 +215,21 @@ def fused_mm_sample(
         status.data_ptr(), stream.cuda_stream,
     )
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
-        and not two_stage and B <= 256 \
-        and not return_logprobs  # larger batches run as several launches, then one exchange
+        and not two_stage and B <= 256  # larger batches run as several launches, then one exchange
     with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
-        if return_logprobs:
+        if return_logprobs and fused_tp:
+            # one launch: winners, their logits and the shards' log-sum-exps all travel in the kernel's exchange
+            c = _lib.FmmsCall()
+            c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
+            (c.W_bf16, c.H_bf16, c.temperature, c.temp_stride, c.V_local, c.D, c.B, c.S, c.seed, c.v_global_offset,
+             c.flags, c.ext_noise, c.noise_ld, c.logits_out, c.out_idx, c.out_val, c.workspace, c.workspace_bytes,
+             c.status_dev, c.stream) = common
+            c.flags |= _lib.FLAG_LOGPROB
+            c.out_logprob, c.out_lse = logprobs.data_ptr(), lse.data_ptr()
+            c.tp_rank, c.tp_world, c.tp_max_items = tp.rank, tp.size, exchange.max_items
+            c.tp_peer_buffers, c.tp_epoch = exchange.ptrs, exchange.next_epoch()
+            rc = lib.fmms_run(ctypes.byref(c))
+        elif return_logprobs:
             rc = lib.fmms_sample_logprobs(*common, logprobs.data_ptr(), lse.data_ptr())
         elif fused_tp:
             # one launch: the sampling kernel's last CTA runs the NVLink exchange itself
@@ -228,7 +239,7 @@ def fused_mm_sample(
             rc = lib.fmms_sample(*common)
     _lib.check(rc, "fmms_sample_tp" if fused_tp else "fmms_sample")
 
-    if tp.size > 1 and return_logprobs:
+    if tp.size > 1 and return_logprobs and not fused_tp:
         # every rank holds its shard's winner, that winner's log-probability under the shard's
         # own normaliser, and the normaliser: gather all three and renormalise
         from .tensor_parallel import reduce_gathered_logprobs

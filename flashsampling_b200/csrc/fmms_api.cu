@@ -590,8 +590,9 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
   if (v_global_offset < 0) return FMMS_ERR_BAD_ARG;
   if (flags & FMMS_FLAG_LOGPROB) {
     if (!out_logprob) return FMMS_ERR_BAD_ARG;
-    // the log-sum-exp is merged on one GPU and decoded by the last CTA
-    if (tpa || (flags & FMMS_FLAG_TWO_STAGE)) return FMMS_ERR_UNSUPPORTED;
+    // the log-sum-exp is merged and decoded by the last CTA (under tensor parallelism after the
+    // exchange of the shards' partial sums), which the stand-alone second stage does not do
+    if (flags & FMMS_FLAG_TWO_STAGE) return FMMS_ERR_UNSUPPORTED;
   }
   if (D % 8 != 0 || ((uintptr_t)W_bf16 & 15) || ((uintptr_t)H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
   if (B > kMaxBatchPerLaunch) {

@@ -87,7 +87,7 @@ __device__ __forceinline__ void stamp(const SampleParams& p, int slot) {
 // Log-probability of a decoded winner (kFlagLogprob): the perturbed value minus the winner's
 // own noise, which is a pure function of (seed, draw, row, id), gives logit / T; the row's
 // log-sum-exp slot gives the normaliser.
-__device__ __forceinline__ float winner_logprob(const SampleParams& p, int b, int s, float y, int idx, float lse) {
+__device__ __forceinline__ float winner_logit(const SampleParams& p, int b, int s, float y, int idx) {
   if (idx < 0 || idx >= p.V) return __int_as_float(0x7fc00000);  // no candidate: NaN
   float g = 0.f;
   if (!(p.flags & kFlagGreedy) && p.temperature[(size_t)b * p.temp_stride] > 0.f) {
@@ -99,7 +99,10 @@ __device__ __forceinline__ float winner_logprob(const SampleParams& p, int b, in
       g = gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u));
     }
   }
-  return (y - g) - lse;
+  return y - g;
+}
+__device__ __forceinline__ float winner_logprob(const SampleParams& p, int b, int s, float y, int idx, float lse) {
+  return winner_logit(p, b, s, y, idx) - lse;
 }
 
 template <bool LSE = false, class SyncFn>
@@ -198,12 +201,26 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   const int parity = (int)(epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * p.tp_max_items;
   const TpRecord* mine = p.tp_peers.slots[rank] + (size_t)parity * world * p.tp_max_items;
+  // kFlagLogprob: two more regions - every item's unperturbed winning logit, every row's (m, l)
+  const size_t logit_region = tp_logit_region(world, p.tp_max_items);
+  const size_t lse_region = tp_lse_region(world, p.tp_max_items);
+  const size_t lse_parity = lse_region + (size_t)parity * world * kTpMaxRows;
   for (int item = tid; item < n; item += nthreads) {
     const unsigned long long k = atomicExch(&p.keys[item], 0ull);
     float v;
     int idx;
     cand_key_decode(k, v, idx);
     tp_send(p.tp_peers, world, my_row + item, v, p.v_offset + idx, epoch);
+    if constexpr (LSE) {
+      const int s = item / p.B, b = item - s * p.B;
+      tp_send_words(p.tp_peers, world, logit_region + my_row + item, winner_logit(p, b, s, v, idx), 0u, epoch);
+      if (s == 0) {  // this shard's log-sum-exp of row b
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < lse_k; ++j)
+          lse_merge_packed(m, l, *reinterpret_cast<volatile unsigned long long*>(&p.lse2[(size_t)j * kLseMaxRows + b]));
+        tp_send_words(p.tp_peers, world, lse_parity + (size_t)rank * kTpMaxRows + b, m, __float_as_uint(l), epoch);
+      }
+    }
   }
   if (tid == 0) {
     *p.ticket = 0u;
@@ -212,11 +229,29 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   for (int item = tid; item < n; item += nthreads) {
     float bv;
     long long bi;
-    if (!tp_recv_max(mine, world, p.tp_max_items, item, epoch, p.tp_wait_ns, bv, bi)) {
+    int win = 0;
+    bool ok = tp_recv_max(mine, world, p.tp_max_items, item, epoch, p.tp_wait_ns, bv, bi, &win);
+    const int s = item / p.B, b = item - s * p.B;
+    if constexpr (LSE) {
+      // the winner's logit from the rank that owns it, and the row's normaliser: the shards' partial
+      // sums merged in rank order, so that every rank computes the same bits
+      float logit = 0.f, m = -INFINITY, l = 0.f;
+      TpRecord rec;
+      if (ok) ok = tp_wait_record(p.tp_peers.slots[rank] + logit_region + ((size_t)parity * world + win) * p.tp_max_items + item,
+                                  epoch, p.tp_wait_ns, rec);
+      if (ok) logit = __uint_as_float(rec.val_bits);
+      for (int r = 0; r < world && ok; ++r) {
+        ok = tp_wait_record(p.tp_peers.slots[rank] + lse_parity + (size_t)r * kTpMaxRows + b, epoch, p.tp_wait_ns, rec);
+        if (ok) lse_merge(m, l, __uint_as_float(rec.val_bits), __uint_as_float(rec.idx));
+      }
+      const float lse = ok ? lse_value(m, l) : __int_as_float(0x7fc00000);
+      p.out_logprob[(size_t)b * p.S + s] = ok ? logit - lse : lse;
+      if (s == 0 && p.out_lse) p.out_lse[b] = lse;
+    }
+    if (!ok) {
       if (p.status_dev) atomicExch(p.status_dev, kErrTimeout);
       bi = -1;
     }
-    const int s = item / p.B, b = item - s * p.B;
     p.out_idx[(size_t)b * p.S + s] = bi;
     if (p.out_val) p.out_val[(size_t)b * p.S + s] = bv;
   }

@@ -1,6 +1,9 @@
 // Tensor-parallel exchange of per-row winners over NVLink peer memory.
 //
-// Every rank owns a symmetric buffer `slots[2][world][max_items]` of 16-byte records.  A record
+// Every rank owns a symmetric buffer of 16-byte records in three regions: winners
+// `[2][world][max_items]`, the winners' unperturbed logits `[2][world][max_items]` and the rows'
+// log-sum-exp partials `[2][world][256]` (the last two only travel when log-probabilities are
+// asked for).  A record
 // carries its own validity: {value bits, epoch, global id, epoch}, each half an 8-byte word that
 // NVLink delivers atomically, so no separate flag and no fence is needed (the "low-latency"
 // protocol of collective libraries).  In step `epoch` rank r stores its records into
@@ -17,6 +20,7 @@
 namespace fmms {
 
 constexpr int kTpMaxWorld = 8;
+constexpr int kTpMaxRows = 256;    // batch rows per launch (log-sum-exp records)
 constexpr int kTpFlagStride = 32;  // the buffer ends with world * 128 reserved bytes; the first word is the
                                    // rank's own step counter (used when the caller passes epoch 0)
 
@@ -29,13 +33,21 @@ struct TpPeers {
   TpRecord* slots[kTpMaxWorld];
 };
 
+__host__ __device__ inline size_t tp_record_count(int world, int max_items) {
+  return (size_t)2 * world * ((size_t)2 * max_items + kTpMaxRows);
+}
+
 __host__ __device__ inline size_t tp_buffer_bytes(int world, int max_items) {
-  return (size_t)2 * world * max_items * sizeof(TpRecord) + (size_t)world * kTpFlagStride * 4;
+  return tp_record_count(world, max_items) * sizeof(TpRecord) + (size_t)world * kTpFlagStride * 4;
 }
 
 __host__ __device__ inline size_t tp_counter_offset(int world, int max_items) {
-  return (size_t)2 * world * max_items * sizeof(TpRecord);
+  return tp_record_count(world, max_items) * sizeof(TpRecord);
 }
+
+// first record of the logit region / of the log-sum-exp region of a rank's buffer
+__host__ __device__ inline size_t tp_logit_region(int world, int max_items) { return (size_t)2 * world * max_items; }
+__host__ __device__ inline size_t tp_lse_region(int world, int max_items) { return (size_t)4 * world * max_items; }
 
 // Epoch of this step: the caller's, or (caller passed 0) one more than the count kept in the
 // rank's own buffer, which makes a captured launch replayable: every replay advances by itself.
@@ -60,6 +72,28 @@ __device__ __forceinline__ TpRecord ld_record(const TpRecord* p) {
   return r;
 }
 
+// Send one record (two payload words) to the same place in every rank's buffer.
+__device__ __forceinline__ void tp_send_words(const TpPeers& peers, int world, size_t record, float a, unsigned int b,
+                                              unsigned int epoch) {
+  for (int q = 0; q < world; ++q) st_record(peers.slots[q] + record, a, b, epoch);
+}
+
+// Wait (bounded) until the record at `src` carries this epoch.  Returns false on time-out.
+__device__ __forceinline__ bool tp_wait_record(const TpRecord* src, unsigned int epoch, unsigned long long wait_limit_ns,
+                                               TpRecord& rec) {
+  rec = ld_record(src);
+  unsigned int spins = 0;
+  unsigned long long t0 = 0;
+  while (rec.epoch0 != epoch || rec.epoch1 != epoch) {
+    if ((++spins & 0x3fu) == 0) {
+      if (t0 == 0) t0 = global_timer_ns();
+      else if (global_timer_ns() - t0 > wait_limit_ns) return false;
+    }
+    rec = ld_record(src);
+  }
+  return true;
+}
+
 // Send this rank's record of `item` to every rank.
 __device__ __forceinline__ void tp_send(const TpPeers& peers, int world, size_t row_item, float v, long long gid,
                                         unsigned int epoch) {
@@ -70,7 +104,7 @@ __device__ __forceinline__ void tp_send(const TpPeers& peers, int world, size_t 
 // Returns false on time-out.
 __device__ __forceinline__ bool tp_recv_max(const TpRecord* mine, int world, int max_items, int item,
                                             unsigned int epoch, unsigned long long wait_limit_ns, float& bv,
-                                            long long& bi) {
+                                            long long& bi, int* winner_rank = nullptr) {
   bv = -INFINITY;
   bi = 0x7fffffffffffffffll;
   unsigned long long t0 = 0;
@@ -90,6 +124,7 @@ __device__ __forceinline__ bool tp_recv_max(const TpRecord* mine, int world, int
     if (v > bv || (v == bv && id < bi)) {
       bv = v;
       bi = id;
+      if (winner_rank) *winner_rank = r;
     }
   }
   return true;
