@@ -14,6 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfmms_b200.so"
 
 # status codes / flags (include/fmms_b200.h)
 OK, ERR_TIMEOUT, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(8)
+ERR_TOPK_OVERFLOW = 8
 FLAG_GREEDY, FLAG_EXT_NOISE, FLAG_RETURN_LOGITS, FLAG_FORCE_GEMV, FLAG_FORCE_MMA, FLAG_TWO_STAGE = 1, 2, 4, 8, 16, 32
 FLAG_SEED_DEVICE = 64
 FLAG_LOGPROB = 128
@@ -57,6 +58,10 @@ class FmmsCall(ctypes.Structure):
         ("staging", c_void_p),
         ("staging_bytes", c_size_t),
         ("status_host", c_void_p),
+        ("top_k", c_int),
+        ("top_p", c_float),
+        ("topk_workspace", c_void_p),
+        ("topk_workspace_bytes", c_size_t),
     ]
 
 
@@ -109,6 +114,7 @@ SIGNATURES = {
     ),
     "fmms_run": (c_int, [ctypes.POINTER(FmmsCall)]),
     "fmms_query_staging": (c_int, [c_int, c_int, c_int, ctypes.POINTER(c_size_t)]),
+    "fmms_query_topk_workspace": (c_int, [c_int, c_int, ctypes.POINTER(c_size_t), ctypes.POINTER(c_size_t)]),
     "fmms_last_path": (c_int, []),
     "fmms_l2_sweep": (c_int, [c_void_p, c_size_t, c_void_p]),
     "fmms_debug_stamps": (c_int, [c_void_p]),
@@ -178,6 +184,14 @@ def query_workspace(v_local: int, d: int, b: int, s: int) -> int:
     n = c_size_t(0)
     check(load().fmms_query_workspace(v_local, d, b, s, ctypes.byref(n)), "fmms_query_workspace")
     return int(n.value)
+
+
+def query_topk_workspace(v_local: int, b: int) -> tuple[int, int]:
+    """(bytes with room for the exact second pass, bytes without it)."""
+    full, small = c_size_t(0), c_size_t(0)
+    check(load().fmms_query_topk_workspace(v_local, b, ctypes.byref(full), ctypes.byref(small)),
+          "fmms_query_topk_workspace")
+    return int(full.value), int(small.value)
 
 
 def query_staging(d: int, b: int, s: int) -> int:

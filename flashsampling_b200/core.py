@@ -52,6 +52,21 @@ def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tenso
     return ws
 
 
+_topk_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def _topk_workspace(device: torch.device, stream_id: int, v_local: int, b: int) -> torch.Tensor:
+    """Scratch of the top-k path (candidate lists and the logits of the exact second pass), zeroed once."""
+    key = (device.index, stream_id)
+    need = _lib.query_topk_workspace(v_local, b)[0]
+    ws = _topk_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _topk_workspaces[key] = ws
+        _all_workspaces.append(ws)
+    return ws
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
     st = _status.get(device.index)
     if st is None:
@@ -100,6 +115,8 @@ def fused_mm_sample(
     return_values: bool = False,
     two_stage: bool = False,  # decode the winners in a second kernel instead of the last CTA
     return_logprobs: bool = False,  # also return ln p(sampled id) [B, num_samples] from the same pass
+    top_k: int | None = None,  # sample among the k largest logits of each row only (1..64)
+    top_p: float | None = None,  # with top_k: nucleus cut of the top-k softmax
 ):
     """Sample ``num_samples`` token ids per hidden-state row from softmax(W h / T).
 
@@ -112,6 +129,11 @@ def fused_mm_sample(
     from a running log-sum-exp.  ``p2p_no_overlap`` selects the
     reference's ablation in which the exchange follows the kernel; here the
     exchange always follows the local reduction, so the flag changes nothing.
+
+    ``top_k`` / ``top_p`` restrict every row to its k largest logits and, of those, to the nucleus
+    of mass ``top_p`` (the reference's ``fused_mm_topk_and_sample``, tl_fused_mm_topk.py:25-37):
+    the pass collects the few candidates at or above a running bound of the k-th largest logit
+    and a second small kernel sorts, filters and samples them (``csrc/fmms_topk.cuh``).
 
     With ``tp.size > 1`` every rank passes its own contiguous vocabulary block
     and the same ``hidden_states``, ``temperature`` and ``seed``; all ranks
@@ -169,6 +191,13 @@ def fused_mm_sample(
     if return_logits:
         logits = torch.empty((B, V), dtype=torch.float32, device=dev)
         flags |= _lib.FLAG_RETURN_LOGITS
+    if top_p is not None and top_k is None:
+        raise ValueError("top_p needs top_k (the nucleus is cut from the top-k softmax, as in the reference)")
+    if top_k is not None:
+        if not 1 <= int(top_k) <= 64:
+            raise ValueError("top_k must be between 1 and 64")
+        if tp.size > 1 or return_logits or two_stage or kernel == "gemv":
+            raise ValueError("top_k is not combined with tensor parallelism, return_logits, two_stage or the gemv kernel")
     if kernel == "gemv":
         flags |= _lib.FLAG_FORCE_GEMV
     elif kernel == "mma":
@@ -217,7 +246,20 @@ def fused_mm_sample(
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
         and not two_stage and B <= 256  # larger batches run as several launches, then one exchange
     with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
-        if return_logprobs and fused_tp:
+        if top_k is not None:
+            c = _lib.FmmsCall()
+            c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
+            (c.W_bf16, c.H_bf16, c.temperature, c.temp_stride, c.V_local, c.D, c.B, c.S, c.seed, c.v_global_offset,
+             c.flags, c.ext_noise, c.noise_ld, c.logits_out, c.out_idx, c.out_val, c.workspace, c.workspace_bytes,
+             c.status_dev, c.stream) = common
+            if return_logprobs:
+                c.out_logprob, c.out_lse = logprobs.data_ptr(), lse.data_ptr()
+            tws = _topk_workspace(dev, stream.cuda_stream, V, B)
+            c.top_k = int(top_k)
+            c.top_p = float(top_p) if top_p is not None else 0.0
+            c.topk_workspace, c.topk_workspace_bytes = tws.data_ptr(), tws.numel()
+            rc = lib.fmms_run(ctypes.byref(c))
+        elif return_logprobs and fused_tp:
             # one launch: winners, their logits and the shards' log-sum-exps all travel in the kernel's exchange
             c = _lib.FmmsCall()
             c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
@@ -473,6 +515,7 @@ class PreparedSampler:
 
 PROVIDERS = (
     "fused-b200",
+    "fused-topk",
     "fused-triton",
     "fused-triton-p2p-no-overlap",
     "fused-triton-ret-logits",
@@ -490,6 +533,10 @@ def get_sampler(provider: str, weights: torch.Tensor) -> Sampler:
     """
     if provider in ("fused-b200", "fused-triton"):
         return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, **kw}), weights, {"seed": 0})
+    if provider == "fused-topk":
+        # the reference's provider for fused_mm_topk_and_sample (core.py registry; tests/test_core.py:102-140):
+        # sample(weights, hidden_states, num_samples, temperature, top_k, top_p)
+        return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, **kw}))
     if provider == "fused-triton-p2p-no-overlap":
         return SimpleSampler(lambda **kw: fused_mm_sample(**{"seed": 0, "p2p_no_overlap": True, **kw}), weights,
                              {"seed": 0})

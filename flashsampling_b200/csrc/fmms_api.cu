@@ -16,6 +16,7 @@
 #include "fmms_gemv.cuh"
 #include "fmms_umma.cuh"
 #include "fmms_umma2.cuh"
+#include "fmms_topk.cuh"
 
 namespace fmms {
 
@@ -33,7 +34,7 @@ struct DeviceInfo {
   int cc_major = 0;
   int max_smem_optin = 0;
   bool gemv_attr[2][kGemvMaxBatch + 1] = {};  // [with log-probabilities][batch rows]
-  bool umma_attr[2][8] = {};
+  bool umma_attr[3][8] = {};  // [plain | log-probabilities | top-k][M tiles; 3 = pair kernel]
 };
 
 static std::mutex g_mu;
@@ -291,25 +292,29 @@ struct UmmaMaps {
   CUtensorMap wq, wq1, hm;
 };
 
-template <int MT, bool LSE>
-static int launch_umma_mt_lse(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
-                              cudaStream_t stream) {
-  if (!d.umma_attr[LSE][MT]) {
-    if (cudaFuncSetAttribute(umma_sample_kernel<MT, LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+template <int MT, bool LSE, bool TOPK>
+static int launch_umma_variant(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
+                               cudaStream_t stream) {
+  bool& attr_set = d.umma_attr[TOPK ? 2 : (LSE ? 1 : 0)][MT];
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(umma_sample_kernel<MT, LSE, TOPK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              d.max_smem_optin) != cudaSuccess)
       return kErrCuda;
-    d.umma_attr[LSE][MT] = true;
+    attr_set = true;
   }
-  umma_sample_kernel<MT, LSE><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
+  umma_sample_kernel<MT, LSE, TOPK><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
       mp.wq, mp.wq1, mp.hm, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
+// The kernels that also accumulate the log-sum-exp (kFlagLogprob) or collect top-k candidates
+// (kFlagTopk) are separate instantiations, so that the plain sampling kernels carry none of that code.
 template <int MT>
 static int launch_umma_mt(DeviceInfo& d, const UmmaMaps& mp, SampleParams& p, const UmmaPlan& pl,
                           cudaStream_t stream) {
-  return (p.flags & kFlagLogprob) ? launch_umma_mt_lse<MT, true>(d, mp, p, pl, stream)
-                                  : launch_umma_mt_lse<MT, false>(d, mp, p, pl, stream);
+  if (p.flags & kFlagTopk) return launch_umma_variant<MT, false, true>(d, mp, p, pl, stream);
+  return (p.flags & kFlagLogprob) ? launch_umma_variant<MT, true, false>(d, mp, p, pl, stream)
+                                  : launch_umma_variant<MT, false, false>(d, mp, p, pl, stream);
 }
 
 static int umma_slabs_force() {
@@ -351,7 +356,8 @@ static int build_umma_maps(const void* W, const void* H, const SampleParams& p, 
 static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams& p, cudaStream_t stream,
                        size_t cand_capacity) {
   // Row replicas keep the S > 1 scratch by TMEM lane (128 rows): without room for that, run without them.
-  const int copies_cap = (p.S > 1 && (size_t)128 * p.S > cand_capacity) ? 1 : umma_copies_cap();
+  const int copies_cap =
+      ((p.flags & kFlagTopk) || (p.S > 1 && (size_t)128 * p.S > cand_capacity)) ? 1 : umma_copies_cap();
   UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
                           umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), copies_cap);
   if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
@@ -482,6 +488,7 @@ const char* fmms_strerror(int status) {
     case FMMS_ERR_CUDA: return "CUDA call failed";
     case FMMS_ERR_ARCH: return "device is not compute capability 10.x (sm_100a)";
     case FMMS_ERR_TOO_LARGE: return "batch rows x draws exceeds the built-in scratch (fmms_static_max_items)";
+    case FMMS_ERR_TOPK_OVERFLOW: return "a row's top-k candidate list overflowed and no scratch for the exact pass was given";
     default: return "unknown status";
   }
 }
@@ -775,6 +782,136 @@ int fmms_query_staging(int D, int B, int S, size_t* bytes) {
   return FMMS_OK;
 }
 
+// ---- top-k / top-p -----------------------------------------------------------------------
+// Scratch layout: a head that is zero between calls, laid out for 256 rows whatever the batch (calls of
+// different batch sizes share one scratch, and the parts behind the head keep stale data):
+// [table 256 x 64 u32][count 256 x 128 B][gbar, need_fallback: 256 B][row_fallback 256][ids of the
+// conditional pass 256 x 8], then [lists B x 4096 x 8][logits B x V x 4].
+struct TopkLayout {
+  size_t table, count, words, rows, dummy_idx, list, logits, total_small, total_full;
+};
+static TopkLayout topk_layout(int V, int B) {
+  TopkLayout l{};
+  size_t off = 0;
+  const size_t rows = kMaxBatchPerLaunch;
+  l.table = off;     off += align256(rows * kTopkSlots * 4);
+  l.count = off;     off += align256(rows * kTopkCountStride * 4);
+  l.words = off;     off += 256;
+  l.rows = off;      off += align256(rows);
+  l.dummy_idx = off; off += align256(rows * 8);
+  l.list = off;      off += align256((size_t)B * kTopkListCap * 8);
+  l.total_small = off;
+  l.logits = off;    off += align256((size_t)B * V * 4);
+  l.total_full = off;
+  return l;
+}
+
+int fmms_query_topk_workspace(int V_local, int B, size_t* bytes, size_t* bytes_without_exact_pass) {
+  if (!bytes || V_local <= 0 || B <= 0) return FMMS_ERR_BAD_ARG;
+  const TopkLayout l = topk_layout(V_local, B > kMaxBatchPerLaunch ? kMaxBatchPerLaunch : B);
+  *bytes = l.total_full;
+  if (bytes_without_exact_pass) *bytes_without_exact_pass = l.total_small;
+  return FMMS_OK;
+}
+
+// One block of at most 256 rows: candidate pass, finish, conditional exact pass.
+static int topk_rows(const fmms_call_t& c, int b0, int nb) {
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != kOk) return rc;
+  if (d->cc_major != 10) return FMMS_ERR_ARCH;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(c.stream);
+  const TopkLayout l = topk_layout(c.V_local, nb);
+  if (c.topk_workspace_bytes < l.total_small) return FMMS_ERR_WORKSPACE;
+  const bool exact_pass = c.topk_workspace_bytes >= l.total_full;
+  unsigned char* tw = reinterpret_cast<unsigned char*>(c.topk_workspace);
+  unsigned char* ws = reinterpret_cast<unsigned char*>(c.workspace);
+
+  SampleParams p{};
+  p.H = reinterpret_cast<const __nv_bfloat16*>(c.H_bf16) + (size_t)b0 * c.D;
+  p.temperature = c.temperature ? c.temperature + (size_t)b0 * c.temp_stride : nullptr;
+  p.temp_stride = c.temp_stride;
+  p.V = c.V_local;
+  p.D = c.D;
+  p.B = nb;
+  p.S = c.S;
+  p.seed = c.seed;
+  p.v_offset = c.v_global_offset;
+  p.flags = (c.flags & (FMMS_FLAG_GREEDY | FMMS_FLAG_EXT_NOISE | FMMS_FLAG_SEED_DEVICE)) | kFlagTopk;
+  p.ext_noise = c.ext_noise ? c.ext_noise + (size_t)b0 * c.noise_ld : nullptr;
+  p.noise_ld = c.noise_ld;
+  p.noise_s_stride = (long long)c.B * c.noise_ld;
+  p.b_offset = b0;
+  p.ticket = reinterpret_cast<unsigned int*>(ws);
+  p.sched = p.ticket + 1;
+  p.keys = reinterpret_cast<unsigned long long*>(ws + kWsHeadBytes);
+  p.cand_val = reinterpret_cast<float*>(ws + kWsHeadBytes + workspace_item_capacity(c.workspace_bytes) * 8);
+  p.cand_idx = reinterpret_cast<int*>(p.cand_val);
+  p.cand_rows = nb;
+  p.lse = reinterpret_cast<unsigned long long*>(ws + kWsLseOffset);
+  p.lse2 = reinterpret_cast<unsigned long long*>(ws + kWsLse2Offset);
+  p.out_idx = c.out_idx + (size_t)b0 * c.S;
+  p.out_val = c.out_val ? c.out_val + (size_t)b0 * c.S : nullptr;
+  p.out_logprob = c.out_logprob ? c.out_logprob + (size_t)b0 * c.S : nullptr;
+  p.out_lse = c.out_lse ? c.out_lse + b0 : nullptr;
+  p.status_dev = c.status_dev;
+  p.stamps = g_stamps;
+  p.tp_world = 1;
+  p.topk.k = c.top_k;
+  p.topk.top_p = c.top_p;
+  p.topk.table = reinterpret_cast<unsigned int*>(tw + l.table);
+  p.topk.count = reinterpret_cast<unsigned int*>(tw + l.count);
+  p.topk.gbar = reinterpret_cast<unsigned int*>(tw + l.words);
+  p.topk.need_fallback = p.topk.gbar + 1;
+  p.topk.row_fallback = tw + l.rows;
+  p.topk.list = reinterpret_cast<unsigned long long*>(tw + l.list);
+
+  // 1. candidate pass (tensor-core kernel, never the CTA-pair variant), 2. one CTA per row finishes
+  int parts = launch_umma(*d, c.W_bf16, p.H, p, stream, 0);
+  if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
+  topk_finish_kernel<<<nb, kTopkFinishThreads, 0, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+  // 3. rows whose list overflowed: a conditional greedy pass writes all logits, then exact selection
+  if (exact_pass) {
+    SampleParams q = p;
+    q.flags = FMMS_FLAG_GREEDY | FMMS_FLAG_RETURN_LOGITS;
+    q.S = 1;
+    q.logits_out = reinterpret_cast<float*>(tw + l.logits);
+    q.out_idx = reinterpret_cast<long long*>(tw + l.dummy_idx);
+    q.out_val = q.out_logprob = q.out_lse = nullptr;
+    q.run_if = p.topk.need_fallback;
+    q.topk = TopkArgs{};
+    parts = launch_umma(*d, c.W_bf16, p.H, q, stream, 0);
+    if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
+    topk_exact_kernel<<<nb, kTopkExactThreads, 0, stream>>>(p, q.logits_out);
+  } else {
+    topk_overflow_kernel<<<nb, 128, 0, stream>>>(p);
+  }
+  g_last_path = FMMS_PATH_MMA;
+  return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
+
+static int topk_impl(const fmms_call_t& c) {
+  g_last_path = FMMS_PATH_NONE;
+  if (!c.W_bf16 || !c.H_bf16 || !c.out_idx || c.V_local <= 0 || c.D <= 0 || c.B <= 0 || c.S <= 0) return FMMS_ERR_BAD_ARG;
+  if (c.top_k < 1 || c.top_k > kTopkSlots) return FMMS_ERR_UNSUPPORTED;
+  const bool greedy = c.flags & FMMS_FLAG_GREEDY, ext = c.flags & FMMS_FLAG_EXT_NOISE;
+  if (!greedy && !c.temperature) return FMMS_ERR_BAD_ARG;
+  if (c.temp_stride != 0 && c.temp_stride != 1) return FMMS_ERR_BAD_ARG;
+  if (ext && !greedy && (!c.ext_noise || c.noise_ld < c.V_local)) return FMMS_ERR_BAD_ARG;
+  if (c.tp_world > 1 || (c.flags & (FMMS_FLAG_RETURN_LOGITS | FMMS_FLAG_TWO_STAGE | FMMS_FLAG_HOST_IO | FMMS_FLAG_FORCE_GEMV)))
+    return FMMS_ERR_UNSUPPORTED;
+  if (c.D % 8 != 0 || ((uintptr_t)c.W_bf16 & 15) || ((uintptr_t)c.H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
+  if (!c.workspace || c.workspace_bytes < workspace_bytes_for(1, 1) || ((uintptr_t)c.workspace & 255)) return FMMS_ERR_WORKSPACE;
+  if (!c.topk_workspace || ((uintptr_t)c.topk_workspace & 255)) return FMMS_ERR_WORKSPACE;
+  for (int b0 = 0; b0 < c.B; b0 += kMaxBatchPerLaunch) {
+    const int nb = c.B - b0 < kMaxBatchPerLaunch ? c.B - b0 : kMaxBatchPerLaunch;
+    const int rc = topk_rows(c, b0, nb);
+    if (rc != FMMS_OK) return rc;
+  }
+  return FMMS_OK;
+}
+
 // Device-visible address of a host pointer (pinned or registered memory under unified addressing),
 // or null for pageable memory.  Asked afresh on every call: an address that was pinned memory once
 // may be pageable memory later.
@@ -798,6 +935,7 @@ __global__ void stage_host_inputs_kernel(const uint4* __restrict__ h_src, uint4*
 
 int fmms_run(const fmms_call_t* c) {
   if (!c || c->struct_bytes != sizeof(fmms_call_t)) return FMMS_ERR_BAD_ARG;
+  if (c->top_k != 0) return topk_impl(*c);
   const int kernel_flags = c->flags & ~(FMMS_FLAG_HOST_IO | FMMS_FLAG_NO_SYNC);
   TpArgs tpa{c->tp_rank, c->tp_world, c->tp_max_items, c->tp_peer_buffers, c->tp_epoch, c->tp_wait_limit_ns};
   const TpArgs* tp = c->tp_world > 1 ? &tpa : nullptr;

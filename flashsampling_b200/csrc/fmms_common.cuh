@@ -17,7 +17,29 @@ constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kEr
 constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
               kFlagForceMma = 16, kFlagTwoStage = 32, kFlagSeedDev = 64, kFlagLogprob = 128;
 
+constexpr int kFlagTopk = 1024;  // internal: the launch collects top-k candidates instead of sampling
+
 constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"
+
+// ------------------------------------------------------------------------------------
+// Top-k / top-p: per-row scratch shared by the candidate-collecting pass and the kernels
+// that finish the rows (see fmms_topk.cuh).  Everything here is zero between calls.
+// ------------------------------------------------------------------------------------
+constexpr int kTopkSlots = 64;       // class maxima per row; also the largest top_k
+constexpr int kTopkListCap = 8192;   // candidates a row's list can hold
+constexpr int kTopkCountStride = 32; // words between two rows' counters: one 128-byte line each, so that
+                                     // the appends of different rows do not queue up behind one L2 line
+struct TopkArgs {
+  int k;                        // top_k (1..kTopkSlots); 0 = off
+  float top_p;                  // nucleus mass in (0, 1); anything else = off
+  unsigned int* table;          // [B][kTopkSlots] order-preserving keys of class maxima (0 = empty)
+  unsigned int* count;          // [B][kTopkCountStride] (first word used) candidates appended so far; above
+                                // the capacity means overflow
+  unsigned long long* list;     // [B][kTopkListCap] packed (scaled logit, local id)
+  unsigned int* gbar;           // grid-wide arrival counter of the collecting pass
+  unsigned int* need_fallback;  // != 0: some row overflowed and the exact pass has to run
+  unsigned char* row_fallback;  // [B] rows that overflowed
+};
 
 // Bounded waits: a wait gives up after this many nanoseconds of wall-clock time,
 // records kErrTimeout and lets the kernel run to its end on whatever data it has.
@@ -108,6 +130,15 @@ __device__ __forceinline__ unsigned long long cand_key(float v, int idx) {
   uint32_t b = __float_as_uint(v);
   b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
   return ((unsigned long long)b << 32) | (unsigned long long)(~(uint32_t)idx);
+}
+
+// The value half of a candidate key on its own: an order-preserving 32-bit image of a float.
+__device__ __forceinline__ uint32_t float_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float float_key_decode(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
 __device__ __forceinline__ void cand_key_decode(unsigned long long k, float& v, int& idx) {

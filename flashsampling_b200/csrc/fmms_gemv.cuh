@@ -75,6 +75,9 @@ struct SampleParams {
   unsigned int tp_epoch;
   unsigned long long tp_wait_ns;
   TpPeers tp_peers;
+  // top-k / top-p (kFlagTopk): the pass collects candidates, other kernels finish the rows
+  TopkArgs topk;
+  const unsigned int* run_if;  // optional: the kernel returns at once when this word is zero
 };
 
 // Last step of a sampling kernel, run by `nthreads` threads of every CTA after their packed

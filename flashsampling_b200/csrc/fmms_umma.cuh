@@ -370,6 +370,47 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
   }
 }
 
+// kFlagTopk: scan columns [c_begin, c_end) of the accumulator tile: z = logit / T; track the largest z
+// seen (`tmax`) and, when `append`, add every z >= pivot to the row's candidate list.
+template <int CW = 32>
+__device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr, int c_begin,
+                                                  int c_end, int v0, float pivot, bool append, float& tmax) {
+  for (int c = c_begin; c < c_end; c += CW) {
+    uint32_t acc[CW];
+    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
+    if (e.row_ok) {
+      const int vbase = v0 + c;
+#pragma unroll
+      for (int i = 0; i < CW; ++i) {
+        if (c + i < c_end && vbase + i < p.V) {
+          const float z = __uint_as_float(acc[i]) * e.inv_t;
+          tmax = fmaxf(tmax, z);
+          if (append && z >= pivot) {
+            const unsigned int pos = atomicAdd(&p.topk.count[(size_t)e.b * kTopkCountStride], 1u);
+            if (pos < (unsigned int)kTopkListCap)
+              p.topk.list[(size_t)e.b * kTopkListCap + pos] = cand_key(z, vbase + i);
+          }
+        }
+      }
+    }
+  }
+}
+
+// The row's pivot: the smallest of its class maxima.  Every class maximum is a different vocabulary
+// entry, so at least kTopkSlots entries are >= the pivot and the top_k-th largest logit
+// (top_k <= kTopkSlots) cannot lie below it.  An empty class means no bound yet (-inf).
+__device__ __forceinline__ float topk_row_pivot(const SampleParams& p, int b) {
+  const uint4* t = reinterpret_cast<const uint4*>(p.topk.table + (size_t)b * kTopkSlots);
+  uint32_t lo = 0xffffffffu;
+#pragma unroll
+  for (int i = 0; i < kTopkSlots / 4; ++i) {
+    uint4 q;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(t + i));
+    lo = min(min(lo, q.x), min(q.y, min(q.z, q.w)));
+  }
+  return lo == 0u ? -INFINITY : float_key_decode(lo);
+}
+
 // Columns [c_begin, c_end) of the range [r_begin, r_end) that column group `g` of `groups` scans:
 // whole CW-column chunks, dealt out evenly.
 template <int CW>
@@ -381,11 +422,12 @@ __device__ __forceinline__ void group_columns(int r_begin, int r_end, int g, int
 }
 
 // ---- the kernel ------------------------------------------------------------------
-template <int MT, bool LSE = false>
+template <int MT, bool LSE = false, bool TOPK = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
                    const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
                    const int units_total, const int q_units, const int h_rows, const int SK, const int R_) {
+  if (p.run_if && *reinterpret_cast<const volatile unsigned int*>(p.run_if) == 0u) return;  // conditional launch
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
@@ -401,7 +443,8 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   uint64_t* empty_bar = full_bar + stages;
   uint64_t* acc_full = empty_bar + stages;
   uint64_t* acc_empty = acc_full + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 4);
+  uint64_t* epi_bar = acc_empty + 4;  // two barriers of the epilogue warps (top-k: before / after the grid-wide wait)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -418,6 +461,8 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kUmmaEpiWarps);
     }
+    mbar_init(&epi_bar[0], kUmmaEpiWarps);
+    mbar_init(&epi_bar[1], kUmmaEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
     stamp(p, 0);
@@ -428,7 +473,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   }
   // S > 1 keeps the running candidates of each (row, draw) in global memory: one row per CTA and
   // epilogue warpgroup, which start as "none"
-  if (p.S > 1) {
+  if (!TOPK && p.S > 1) {
     const int n = kUmmaEpiGroups * p.S * p.cand_rows;
     float* cv = p.cand_val + (size_t)cta * n;
     int* ci = p.cand_idx + (size_t)cta * n;
@@ -601,6 +646,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     float best_val = -INFINITY;  // S == 1: lives in registers for the whole kernel
     int best_idx = kIdxNone;
     float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
+    bool topk_started = false;             // kFlagTopk: the CTA's first tile has been through the grid-wide step
 
     TileWalk walk(units_total, n_tiles);
     for (int t = 0, ta = 0; t < n_tiles; ++t) {
@@ -618,7 +664,51 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       if (!mbar_wait(&acc_full[j], un & 1u, abort_flag, p.status_dev)) break;
       tc_fence_after();
       if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
-      if (warp_ok) {
+      if constexpr (TOPK) {
+        // Candidates for top-k: everything at or above the row's pivot goes into the row's list.  The
+        // pivot is the smallest of kTopkSlots class maxima, to which every (CTA, warpgroup, tile)
+        // contributes the largest scaled logit it has seen.  The first tile is scanned twice: once
+        // for its maxima, then - after every CTA of the grid has published its own - for the
+        // candidates; later tiles refresh the pivot, append, and publish their maximum afterwards.
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
+        // odd multipliers: every row reaches all slots, and every slot hears from all column groups (whose
+        // shares of a tile differ in width), so that no class is made of narrow shares only
+        const int slot = (cta * 5 + (m_tile * kColGroups + col_group) * 17 + 37 * t) & (kTopkSlots - 1);
+        float tmax = -INFINITY;
+        if (!topk_started) {
+          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, 0.f, false, tmax);
+          if (row_ok && tmax > -INFINITY) atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&epi_bar[0]);
+          bool ok = mbar_wait(&epi_bar[0], 0u, abort_flag, p.status_dev);
+          if (ok && ew == 0 && lane == 0) {
+            // grid-wide: all CTAs are resident (one per SM), so every one of them arrives
+            atomicAdd(p.topk.gbar, 1u);
+            const unsigned long long t0 = global_timer_ns();
+            unsigned int spins = 0;
+            while (*reinterpret_cast<volatile unsigned int*>(p.topk.gbar) < gridDim.x) {
+              if ((++spins & 0xffu) == 0 && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
+                *abort_flag = 1;
+                if (p.status_dev) atomicExch(p.status_dev, kErrTimeout);
+                break;
+              }
+            }
+            __threadfence();
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&epi_bar[1]);
+          ok = ok && mbar_wait(&epi_bar[1], 0u, abort_flag, p.status_dev);
+          if (!ok) break;
+          topk_started = true;
+          const float pivot = row_ok ? topk_row_pivot(p, b) : INFINITY;
+          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, tmax);
+        } else {
+          const float pivot = row_ok ? topk_row_pivot(p, b) : INFINITY;
+          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, tmax);
+          if (row_ok && tmax > -INFINITY) atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
+        }
+      } else if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         if constexpr (LSE) {
           if (narrow) lse_tile_columns<16>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
@@ -653,7 +743,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     if (ew == 0 && lane == 0) stamp(p, 5);
     // merge this thread's winners into the per-(row, draw) keys
-    if (row_ok) {
+    if (!TOPK && row_ok) {
       if (S == 1) {
         if (best_idx != kIdxNone) atomicMax(&p.keys[b], cand_key(best_val, best_idx));
       } else {
@@ -688,7 +778,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       p.lse[(size_t)cta * p.B + r] = lse_pack(m, l);
     }
   }
-  if (!(p.flags & kFlagTwoStage)) {
+  if (!TOPK && !(p.flags & kFlagTwoStage)) {
     volatile int* is_last = abort_flag + 1;
     finish_sample<LSE>(p, tid, kUmmaThreads, [] { __syncthreads(); }, is_last, /*fenced_and_synced=*/!LSE);
   }

@@ -37,6 +37,8 @@ extern "C" {
 #define FMMS_ERR_CUDA 5          /* a CUDA runtime/driver call failed           */
 #define FMMS_ERR_ARCH 6          /* device is not compute capability 10.x       */
 #define FMMS_ERR_TOO_LARGE 7     /* B * S exceeds the built-in scratch          */
+#define FMMS_ERR_TOPK_OVERFLOW 8 /* status word only: a row's top-k candidates overflowed and no scratch
+                                    for the exact second pass was given (see fmms_query_topk_workspace) */
 
 /* flags of fmms_sample / fmms_sample_tp */
 #define FMMS_FLAG_GREEDY 1         /* argmax of raw logits (core.py GREEDY_SAMPLING, :569-600) */
@@ -233,9 +235,39 @@ typedef struct fmms_call {
   void* staging;
   size_t staging_bytes;
   int* status_host;
+  /* top-k / top-p sampling: top_k in 1..64 switches it on (see fmms_query_topk_workspace) */
+  int top_k;
+  float top_p;              /* nucleus mass in (0, 1); any other value: top-k only */
+  void* topk_workspace;     /* device memory, 256-byte aligned, ZERO before its first use */
+  size_t topk_workspace_bytes;
 } fmms_call_t;
 
 int fmms_run(const fmms_call_t* call);
+
+/*
+ * Top-k / top-p sampling (fmms_run() with call.top_k in 1..64).  Replaces the reference's
+ * fused_mm_topk_and_sample(): per-tile top-k lists written by fused_mm_topk_kernel
+ * (tl_fused_mm_topk.py:146-238) and merged, filtered and sampled by _topk_merge_and_sample
+ * (tl_fused_mm_topk.py:76-107).  Same distribution: softmax of logits / T over the k largest
+ * logits of a row, optionally cut to the smallest prefix (in descending order) whose mass before
+ * each kept entry is below top_p (the most probable entry always stays), renormalised.
+ *
+ * Here the tensor-core pass appends to a per-row list only the logits at or above a running
+ * lower bound of the row's k-th largest logit (about 1e3 of 1.5e5 entries); one small kernel per
+ * call then sorts each row's list, applies softmax and the nucleus cut and draws the samples as a
+ * Gumbel-max over the surviving ids, with the noise stream of fmms_sample() (so a draw equals the
+ * unrestricted draw for the same seed whenever that one survives the cut).  A row whose list
+ * overflows (4096 entries; logits that arrive in ascending order do that) is redone exactly by a
+ * second pass that materialises its logits - launched with every call, it returns at once when
+ * no row needs it.  out_logprob / out_lse, when given, refer to the truncated distribution.
+ *
+ * The scratch: `bytes` includes room for those logits (B x V_local x 4); with only
+ * `bytes_without_exact_pass` an overflowing row gets ids of -1 and FMMS_ERR_TOPK_OVERFLOW in the
+ * status word instead.  Zero the memory once; every call leaves it ready for the next.
+ * Not combined with tensor parallelism, FMMS_FLAG_RETURN_LOGITS, FMMS_FLAG_TWO_STAGE or
+ * FMMS_FLAG_HOST_IO (FMMS_ERR_UNSUPPORTED).
+ */
+int fmms_query_topk_workspace(int V_local, int B, size_t* bytes, size_t* bytes_without_exact_pass);
 
 /* Bytes of device staging that fmms_run() needs with FMMS_FLAG_HOST_IO for B rows of D hidden
  * values and S draws. No reference counterpart. */
