@@ -338,16 +338,31 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
             }
           }
         }
+      } else if (!e.noisy) {
+        // a row with temperature <= 0 inside a sampled batch: plain argmax, no noise to draw
+#pragma unroll
+        for (int i = 0; i < CW; ++i) {
+          const float y = __uint_as_float(acc[i]) * e.inv_t;
+          if (c + i < c_end && vbase + i < p.V && y > bv) {
+            bv = y;
+            bi = vbase + i;
+          }
+        }
       } else if (e.quad_aligned) {
         const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
 #pragma unroll
         for (int g = 0; g < CW / 4; ++g) {
           const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+          // (A cheap screen in front of the exact comparison - the leading random bits against
+          // 2^((x / T - best) log2 e), one ex2 instead of a conversion and two logarithms, exact path for the
+          // survivors - was measured and dropped: the last tile of a 5-tile range got 16 % faster, but a
+          // CTA's first tile, where new records are frequent and the warp runs both paths, got 14 %
+          // slower, and short tensor-parallel shards consist of that tile alone.)
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {
             const int i = g * 4 + wi;
-            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(w[wi]) : 0.f);
+            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
             if (c + i < c_end && vbase + i < p.V && y > bv) {
               bv = y;
               bi = vbase + i;
