@@ -305,6 +305,16 @@ def run_b200(args):
 
             both, _ = time_steps(alternating_step, 2 * n_pair, 6, sweep_read, barrier)  # even warm-up keeps the parity
             pair["pair_plain_ms"], pair["pair_logprob_ms"] = both[0::2], both[1::2]
+        if with_e2e and world == 1 and t.ndim == 0:
+            # top-k / top-p sampling from the same pass (k = 50, p = 0.9: the defaults engines ship with), same protocol
+            def topk_step():
+                seed[0] += S
+                turn[0] += 1
+                return fs.fused_mm_sample(ws[turn[0] % n_copies], h, S, t, seed=seed[0], top_k=50, top_p=0.9)
+
+            topk_step()
+            tk, _ = time_steps(topk_step, max(20, steps // 4), 5, sweep_read, barrier)
+            pair["topk_ms"] = tk
         if with_e2e:
             h_host = h.cpu().pin_memory()
             t_host = t.cpu().reshape(-1).pin_memory()
@@ -473,6 +483,11 @@ def run_b200(args):
             "note": "the step with return_logprobs=True (log-probability of every sampled id from the same pass) and the "
                     "plain step, alternating call by call inside one timed window (same per-call protocol as `value`)",
         }} if "pair_logprob_ms" in main else {}),
+        **({"top_k_top_p": {
+            "us": round(statistics.median(main["topk_ms"]) * 1e3, 3), "top_k": 50, "top_p": 0.9,
+            "note": "the step with top_k=50, top_p=0.9 (candidate pass + per-row finish kernel + the two conditional "
+                    "launches of the exact pass, which return at once), per-call CUDA events like `value`",
+        }} if "topk_ms" in main else {}),
         "env": {"gpu": torch.cuda.get_device_name(device), "torch": torch.__version__, "cuda": torch.version.cuda},
         **({"tp_ids_equal_unsharded": main["tp_equal"]} if main["tp_equal"] is not None else {}),
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
@@ -500,6 +515,9 @@ def run_b200(args):
         line["sweep"] = sweep
     if triton_ref is not None:
         mine = triton_ref.get(B) if "unavailable" not in triton_ref else None
+        if mine and "top_k_top_p" in line and "topk_us" in mine:
+            line["top_k_top_p"]["reference_us"] = mine["topk_us"]
+            line["top_k_top_p"]["speedup_vs_reference"] = round(mine["topk_us"] / line["top_k_top_p"]["us"], 2)
         line["reference_triton"] = (
             {"us": mine["us"], "write_flush_us": mine["write_flush_us"],
              "note": "the reference's own Triton kernel (fused_mm_sample_triton, installed copy under baseline/_ref) on "
@@ -580,6 +598,20 @@ def run_triton_leg(args):
             entry.update(us=round(statistics.median(a) * 1e3, 2), write_flush_us=round(statistics.median(b) * 1e3, 2))
         except Exception as exc:  # a shape the reference's kernel refuses: report, go on
             entry["unavailable"] = f"{type(exc).__name__}: {str(exc)[:200]}"
+        if B == args.batch and S == 1:
+            # the reference's top-k path (fused_mm_topk_and_sample: per-tile top-k lists, torch top-k, multinomial)
+            try:
+                from fused_mm_sampling.tl_fused_mm_topk import fused_mm_topk_and_sample
+
+                def topk_step():
+                    return fused_mm_topk_and_sample(w, h, S, t, 50, 0.9)
+
+                topk_step()
+                torch.cuda.synchronize()
+                c, _ = time_steps(topk_step, max(10, args.steps // 2), 3, sweep_read, lambda: None)
+                entry["topk_us"] = round(statistics.median(c) * 1e3, 2)
+            except Exception as exc:
+                entry["topk_unavailable"] = f"{type(exc).__name__}: {str(exc)[:200]}"
         out.append(entry)
     print(json.dumps({"triton_leg": out}), flush=True)
 
@@ -670,10 +702,78 @@ def run_once(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     for i in range(5):
         _lib.load().fmms_l2_sweep(flush.data_ptr(), flush.numel(), torch.cuda.current_stream().cuda_stream)
-        fs.fused_mm_sample(w, h, wl["S"], t, seed=i, kernel=args.kernel)
+        fs.fused_mm_sample(w, h, wl["S"], t, seed=i, kernel=args.kernel, top_k=args.top_k or None,
+                           top_p=(args.top_p or None) if args.top_k else None)
     torch.cuda.synchronize()
     fs.check_status()
-    print(json.dumps({"once": True, "workload": args.workload, "batch": args.batch, "kernel": fs.last_path()}))
+    print(json.dumps({"once": True, "workload": args.workload, "batch": args.batch, "kernel": fs.last_path(),
+                      "top_k": args.top_k, "top_p": args.top_p}))
+
+
+def run_stamps(args):
+    """--stamps: the per-phase %globaltimer stamps of the sampling kernel (fmms_debug_stamps) for one
+    workload, one table line per rank.  Works on one GPU and under torchrun (tensor parallel)."""
+    import numpy as np
+    import torch.distributed as dist
+
+    import flashsampling_b200 as fs
+    from flashsampling_b200 import _lib, build
+    from flashsampling_b200.tp_info import TPInfo
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    build.build_library()
+    lib = _lib.load()
+    wl = WORKLOADS[args.workload]
+    tp = TPInfo(rank=rank, size=world, vocab_size=wl["V"])
+    w, h, t = make_inputs(wl, args.batch, rank, world, device)
+    sampler = fs.get_sampler("fused-b200", w).prepare()
+    flush = torch.empty(768 << 20, dtype=torch.uint8, device=device)
+    stamps = torch.zeros(320 * 8, dtype=torch.int64, device=device)
+    align = torch.zeros(1, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step(i):
+        return sampler.sample(hidden_states=h, num_samples=wl["S"], temperature=t, seed=i, tp=tp)
+
+    for i in range(10):
+        step(i)
+    torch.cuda.synchronize()
+    rows = []
+    for i in range(args.steps if args.steps < 100 else 20):
+        stamps.zero_()
+        lib.fmms_l2_sweep(flush.data_ptr(), flush.numel(), stream)
+        if world > 1:
+            dist.all_reduce(align)  # ranks aligned on the device right before the step
+        lib.fmms_debug_stamps(stamps.data_ptr())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step(100 + i)
+        e1.record()
+        torch.cuda.synchronize()
+        lib.fmms_debug_stamps(None)
+        s = stamps.cpu().numpy().reshape(320, 8).astype(np.float64)
+        s = s[s[:, 0] > 0]
+        t0 = s[:, 0].min()
+        rel = (s - t0) / 1e3
+        rel[s == 0] = np.nan
+        rows.append((e0.elapsed_time(e1) * 1e3, np.nanmedian(rel[:, 2]), np.nanmedian(rel[:, 3]), np.nanmedian(rel[:, 5]),
+                     np.nanmax(rel[:, 6]), np.nanmax(rel[:, 7])))
+    rows.sort()
+    ev, first, mma, epi, done, dec = rows[len(rows) // 2]
+    fs.check_status()
+    print(json.dumps({"stamps_us": {"rank": rank, "n_gpus": world, "workload": args.workload, "batch": args.batch,
+                                    "kernel": fs.last_path(), "first_operands": round(first, 2),
+                                    "last_mma_issued_median_cta": round(mma, 2), "epilogue_done_median_cta": round(epi, 2),
+                                    "last_cta_ticket": round(done, 2), "winners_decoded": round(dec, 2),
+                                    "cuda_event_time": round(ev, 2)}}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -689,12 +789,18 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--once", action="store_true", help="five calls of one configuration, for profilers")
     ap.add_argument("--kernel", default=None, choices=["gemv", "mma"], help="--once: force a kernel")
+    ap.add_argument("--top-k", type=int, default=0, help="--once: sample with top-k (0 = off); the benchmark's top-k leg uses 50")
+    ap.add_argument("--top-p", type=float, default=0.0, help="--once: nucleus mass used with --top-k")
     ap.add_argument("--reference-triton", action=argparse.BooleanOptionalAction, default=True,
                     help="one GPU: also time the reference's Triton kernel (baseline/_ref) in a child process")
     ap.add_argument("--triton-leg", action="store_true", help="child process of --reference-triton")
     ap.add_argument("--batches", default="64", help="--triton-leg: comma-separated batch sizes")
+    ap.add_argument("--stamps", action="store_true",
+                    help="print the kernel's per-phase %%globaltimer stamps for one workload (one JSON line per rank)")
     args = ap.parse_args()
-    if args.triton_leg:
+    if args.stamps:
+        run_stamps(args)
+    elif args.triton_leg:
         run_triton_leg(args)
     elif args.once:
         run_once(args)

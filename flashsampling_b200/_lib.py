@@ -130,6 +130,7 @@ SIGNATURES = {
          c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
     "fmms_static_max_items": (c_int, []),
+    "fmms_static_reset": (c_int, [c_void_p]),
     "fmms_sample_static": (
         c_int,
         [

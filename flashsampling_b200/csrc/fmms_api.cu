@@ -926,7 +926,7 @@ static void* host_ptr_on_device(const void* host) {
 // Hidden states and temperatures from device-visible host memory into the staging buffer: one small
 // kernel in place of two copy-engine operations (each of which costs a hand-over between the copy
 // and the compute engine, several microseconds, before the sampling kernel may start).
-__global__ void stage_host_inputs_kernel(const uint4* __restrict__ h_src, uint4* __restrict__ h_dst, size_t n16,
+static __global__ void stage_host_inputs_kernel(const uint4* __restrict__ h_src, uint4* __restrict__ h_dst, size_t n16,
                                          const float* __restrict__ t_src, float* __restrict__ t_dst, int nt) {
   const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = i0; i < n16; i += stride) h_dst[i] = h_src[i];
@@ -1091,6 +1091,15 @@ int fmms_l2_sweep(const void* buffer, size_t bytes, void* stream) {
 }
 
 int fmms_static_max_items(void) { return kStaticMaxItems; }
+
+int fmms_static_reset(void* stream) {
+  void* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != kOk) return rc;
+  // the part that calls rely on being zero: CTA counter, work counter and the packed winners
+  const size_t head = kWsHeadBytes + (size_t)kStaticMaxItems * 8;
+  return cudaMemsetAsync(scratch, 0, head, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;
+}
 
 int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                        int V_local, int D, int B, int S, unsigned long long seed, long long v_global_offset,

@@ -115,7 +115,17 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
     __threadfence();
     sync();
   }
-  if (tid == 0) *is_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  if (tid == 0) {
+    // Tensor parallel with the step counter kept on the device: fetch it now, so that its latency
+    // overlaps the ticket's (only the CTA that turns out to be last uses it; is_last[1] carries it)
+    unsigned int step = p.tp_epoch;
+    if (p.tp_world > 1 && step == 0u)
+      step = tp_load_counter(reinterpret_cast<const unsigned int*>(
+                 reinterpret_cast<const unsigned char*>(p.tp_peers.slots[p.tp_rank]) +
+                 tp_counter_offset(p.tp_world, p.tp_max_items))) + 1u;
+    *is_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    is_last[1] = (int)step;
+  }
   sync();
   if (tid == 0) stamp(p, 6);
   if (!*is_last) return;
@@ -195,11 +205,11 @@ __device__ __forceinline__ void finish_sample(const SampleParams& p, int tid, in
   // fmms_tp.cuh for the protocol), then the same threads wait for the peers' records and keep
   // the maximum.  Items are processed in rounds of `nthreads`: send a round, then receive it.
   const int world = p.tp_world, rank = p.tp_rank;
-  unsigned int epoch = p.tp_epoch;
+  // this step's number: the caller's, or one more than the count kept in the rank's own buffer (a captured
+  // launch then advances by itself on every replay); fetched by thread 0 before the ticket
+  const unsigned int epoch = (unsigned int)is_last[1];
   unsigned int* counter = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(p.tp_peers.slots[rank]) +
                                                           tp_counter_offset(world, p.tp_max_items));
-  if (epoch == 0u) epoch = tp_load_counter(counter) + 1u;  // step counter kept on the device (replayable)
-  sync();
   if (tid == 0) *counter = epoch;
   const int parity = (int)(epoch & 1u);
   const size_t my_row = ((size_t)parity * world + rank) * p.tp_max_items;

@@ -45,6 +45,23 @@ class FMMSSampler:
         self.tp = tp
         self.device_seed = device_seed
         self._seed_t = None
+        if tp.size > 1 and torch.cuda.is_available():
+            # The exchange buffers are created collectively (IPC handles travel through the process
+            # group, cudaMalloc): do it here, at engine start-up on every rank, not inside the first
+            # sampling call, which may already run under CUDA-graph capture.
+            from .tensor_parallel import get_exchange
+
+            get_exchange(tp, torch.device("cuda", torch.cuda.current_device()))
+
+    @property
+    def status(self) -> torch.Tensor:
+        """The device status word (int32, one element) that a kernel sets when one of its bounded waits
+        runs out - e.g. a tensor-parallel peer that is more than the wait limit late; the ids of that
+        step are then -1.  Nothing on the sampling path synchronises, so the engine tests this word at
+        its own synchronisation point (or calls ``flashsampling_b200.check_status()``, which raises)."""
+        from .core import _status_word
+
+        return _status_word(torch.device("cuda", torch.cuda.current_device()))
 
     def __call__(self, lm_head_weight: torch.Tensor, hidden_states: torch.Tensor,
                  sampling_metadata: SamplingMetadata) -> torch.Tensor:

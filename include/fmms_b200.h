@@ -321,7 +321,11 @@ int fmms_tp_exchange(const long long* local_idx, const float* local_val, int n_i
  *     one stream, or ordered by events, are safe.  The array keeps the last call's
  *     running candidates; the part that must start at zero (packed winners, CTA
  *     counter) is zero when the library is loaded and is zeroed again by each call's
- *     last CTA, so the caller never clears anything.
+ *     last CTA, so the caller never clears anything;
+ *   - after a call whose status word reported FMMS_ERR_TIMEOUT the array is normally clean
+ *     as well (a CTA whose wait ran out still takes its ticket, and the last one still
+ *     clears the head), but a caller that wants certainty - or whose launch was cut short
+ *     from outside - calls fmms_static_reset() before the next sample.
  */
 int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
                        int V_local, int D, int B, int S, unsigned long long seed,
@@ -331,6 +335,11 @@ int fmms_sample_static(const void* W_bf16, const void* H_bf16, const float* temp
 
 /* Largest B * S that fmms_sample_static() accepts. No reference counterpart. */
 int fmms_static_max_items(void);
+
+/* Zero the part of the built-in array that fmms_sample_static() expects to be zero (one
+ * cudaMemsetAsync on `stream`; allocates nothing).  The counterpart of "zero the workspace
+ * again" for callers that own no workspace.  No reference counterpart. */
+int fmms_static_reset(void* stream);
 
 #ifdef __cplusplus
 }

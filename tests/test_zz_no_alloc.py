@@ -44,7 +44,9 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     t = torch.tensor([0.8], device=dev)
     # two calls in a row on the shared scratch: a small batch on the weight-streaming kernel,
     # then a larger one on the tensor-core kernel whose candidate rows overlap the first call's
-    cases = [(6000, 256, 3, 4, 11, _lib.FLAG_FORCE_GEMV), (9000, 512, 200, 2, 12, _lib.FLAG_FORCE_MMA)]
+    # ... then more than 256 rows (consecutive launches through the same array), then a small batch again
+    cases = [(6000, 256, 3, 4, 11, _lib.FLAG_FORCE_GEMV), (9000, 512, 200, 2, 12, _lib.FLAG_FORCE_MMA),
+             (5000, 128, 600, 1, 13, 0), (6000, 256, 2, 3, 14, _lib.FLAG_FORCE_GEMV)]
     for V, D, B, S, seed, flags in cases:
         w, h = gaussian_head(V, D, B, 0.06, seed=seed, device=dev)
         ws = torch.zeros(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=dev)
@@ -54,6 +56,14 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         assert int(ids_b.min()) >= 0 and int(ids_b.max()) < V
         assert torch.equal(ids_a, ids_b)
         assert torch.equal(val_a, val_b)  # same kernels and noise: tolerance zero
+    # the reset entry point (for use after a reported time-out) leaves the array usable
+    assert lib.fmms_static_reset(torch.cuda.current_stream().cuda_stream) == 0
+    V, D, B, S, seed, flags = cases[1]
+    w, h = gaussian_head(V, D, B, 0.06, seed=seed, device=dev)
+    ws = torch.zeros(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=dev)
+    _, ids_a, _ = _call(lib, "fmms_sample", w, h, t, B, S, seed, flags, ws)
+    rc_b, ids_b, _ = _call(lib, "fmms_sample_static", w, h, t, B, S, seed, flags)
+    assert rc_b == 0 and torch.equal(ids_a, ids_b)
     # beyond the built-in scratch: refused with its own status, nothing launched
     limit = lib.fmms_static_max_items()
     B, S = 256, limit // 256 + 1
