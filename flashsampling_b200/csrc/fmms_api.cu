@@ -303,7 +303,7 @@ static int launch_umma_variant(DeviceInfo& d, const UmmaMaps& mp, SampleParams& 
     attr_set = true;
   }
   umma_sample_kernel<MT, LSE, TOPK><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
-      mp.wq, mp.wq1, mp.hm, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies);
+      mp.wq, mp.wq1, mp.hm, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies, pl.m_rows);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
@@ -322,6 +322,10 @@ static int umma_slabs_force() {
   return v;
 }
 
+static int umma_m64() {
+  static const int v = std::getenv("FMMS_UMMA_M64") ? env_int("FMMS_UMMA_M64") : -1;  // 0 / 1 force M = 128 / 64 (B <= 64)
+  return v;
+}
 static int umma_copies_cap() {
   static const int v = env_int("FMMS_UMMA_COPIES");  // 0 (default): no row replicas; 2 / 4: up to that many
   return v;
@@ -370,6 +374,7 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
     rc = build_umma_maps(W, H, p, pl, &mp);
   }
   if (rc != kOk) return -rc;
+  if (umma_m64() >= 0 && pl.mt == 1 && pl.copies == 1 && pl.h_rows <= 64) pl.m_rows = umma_m64() ? 64 : 128;
   if (pl.copies > 1) {
     p.cand_rows = 128;
     p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * 128 * p.S);

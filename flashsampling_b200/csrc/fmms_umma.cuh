@@ -57,6 +57,7 @@ struct UmmaPlan {
   int mt;             // M tiles (1 or 2)
   int slabs;          // 64-column K slabs per pipeline stage (one TMA operation fetches them all)
   int copies;         // row replicas R (1, 2 or 4): MMAs per K step, each over 1/R of the tile's columns
+  int m_rows;         // rows of the MMA's M axis: 128, or 64 for some batches of at most 64 rows (see umma_plan)
   size_t smem;
 };
 
@@ -136,6 +137,12 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   const int low_units = pl.q_units > 1 ? pl.q_units - 1 : pl.q_units;
   while (r > 1 && (size_t)pl.slabs * low_units * 16 * 128 < (size_t)(r - 1) * (16384 / r)) r >>= 1;
   pl.copies = r;
+  // M = 64 MMAs read half the A operand and leave 16 rows in the lower half of every TMEM lane quadrant.  Measured
+  // against M = 128 in the same run (Qwen head): B = 4 210 -> 200 us, B = 16 203.7 -> 199.7, B = 64 217 -> 213
+  // (last-tile epilogue 9.5 -> 6.9 us), Llama head B = 64 367 -> 351; but B = 32 203.6 -> 213.7: every step with
+  // two or more active lane quadrants is ~10 us slower than one with a single quadrant, whatever M is, and M = 64
+  // spreads 17..32 rows over two quadrants where M = 128 keeps them in one.
+  pl.m_rows = (pl.mt == 1 && r == 1 && (pl.h_rows <= 16 || (pl.h_rows > 32 && pl.h_rows <= 64))) ? 64 : 128;
   return pl;
 }
 
@@ -222,9 +229,9 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
   return d;
 }
 
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
-__host__ __device__ inline uint32_t umma_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128 (or 64).
+__host__ __device__ inline uint32_t umma_idesc(int n, int m = 128) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -441,13 +448,20 @@ template <int MT, bool LSE = false, bool TOPK = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_constant__ CUtensorMap w_map_q1,
                    const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
-                   const int units_total, const int q_units, const int h_rows, const int SK, const int R_) {
+                   const int units_total, const int q_units, const int h_rows, const int SK, const int R_,
+                   const int m_rows) {
   if (p.run_if && *reinterpret_cast<const volatile unsigned int*>(p.run_if) == 0u) return;  // conditional launch
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int n_tiles = p.tiles_per_cta;  // tiles of zero rows (tiny vocabularies) are skipped
   const int R = (MT == 1) ? R_ : 1;     // row replicas (see the head of this file)
+  // M = 64 (MT = 1, at most 64 batch rows, no replicas): accumulator row i sits in TMEM lane 32 * (i / 16) + i % 16,
+  // i.e. 16 rows in the lower half of every lane quadrant
+  const bool m64 = (MT == 1) && m_rows == 64;
+  // The non-epilogue warps.  (Moving the MMA issuer and the W producer to the warps whose schedulers have no
+  // epilogue rows at B <= 64 was measured: no difference.)
+  constexpr int mma_warp = 1, w_warp = 0, h_warp = 2;
   // stage = [SK W slabs][MT x SK hidden-state slabs]; SK > 1 means the maps are 3-D (slab = dim 2)
   const size_t h_slab_bytes = (size_t)h_rows * 128;
   const size_t stage_bytes = umma_stage_bytes(MT, q_units, h_rows, SK);
@@ -482,7 +496,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     fence_mbar_init();
     stamp(p, 0);
   }
-  if (warp == 1) {
+  if (warp == mma_warp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -503,13 +517,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   if (tid == 0) stamp(p, 1);
 
-  if (warp == 0 || warp == 2) {
+  if (warp == w_warp || warp == h_warp) {
     // ------------------------------ TMA producers -----------------------------
     // Two threads issue the loads of a stage, warp 0 the W tile and warp 2 the
     // hidden-state tile(s): a single thread sustains only about three bulk-tensor
     // operations per microsecond, which would cap the weight stream.
     if (lane == 0) {
-      const bool is_w = (warp == 0);
+      const bool is_w = (warp == w_warp);
       if (is_w) {
         prefetch_tmap(&w_map_q);
         prefetch_tmap(&w_map_q1);
@@ -557,7 +571,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == mma_warp) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       int it = 0;
@@ -595,7 +609,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
                 if (ce == cb) continue;
                 const uint64_t adesc = umma_smem_desc(a_slab - (uint32_t)r * a_shift);
                 const uint64_t bdesc = umma_smem_desc(w_slab + (uint32_t)(cb * 128));
-                const uint32_t idesc = umma_idesc(ce - cb);
+                const uint32_t idesc = umma_idesc(ce - cb, m64 ? 64 : 128);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap + cb);
 #pragma unroll
                 for (int k = 0; k < kUmmaBK / 16; ++k)
@@ -637,9 +651,9 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     // the replica whose rows sit in this quadrant's lanes, and the batch row of this thread
     const int lanes_per_replica = 128 / R;
     const int replica = (quad * 32) / lanes_per_replica;
-    const int b = m_tile * 128 + quad * 32 + lane - replica * lanes_per_replica;
-    const bool row_ok = b < p.B;
-    const bool warp_ok = (m_tile * 128 + quad * 32 - replica * lanes_per_replica) < p.B;
+    const int b = m64 ? quad * 16 + lane : m_tile * 128 + quad * 32 + lane - replica * lanes_per_replica;
+    const bool row_ok = m64 ? (lane < 16 && b < p.B) : b < p.B;
+    const bool warp_ok = m64 ? quad * 16 < p.B : (m_tile * 128 + quad * 32 - replica * lanes_per_replica) < p.B;
     const int cand_row = (R > 1) ? quad * 32 + lane : b;  // row of the S > 1 scratch: replicas must not share one
 
     const bool greedy = (p.flags & kFlagGreedy) != 0;
@@ -779,7 +793,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   tc_fence_before();
   __threadfence();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == mma_warp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
