@@ -20,6 +20,7 @@ FLAG_SEED_DEVICE = 64
 FLAG_LOGPROB = 128
 FLAG_HOST_IO = 256
 FLAG_NO_SYNC = 512
+FLAG_W_FP8 = 2048
 PATH_NONE, PATH_GEMV, PATH_MMA = 0, 1, 2
 
 class FmmsCall(ctypes.Structure):
@@ -62,6 +63,7 @@ class FmmsCall(ctypes.Structure):
         ("top_p", c_float),
         ("topk_workspace", c_void_p),
         ("topk_workspace_bytes", c_size_t),
+        ("w_scale", c_void_p),
     ]
 
 

@@ -67,6 +67,19 @@ def _topk_workspace(device: torch.device, stream_id: int, v_local: int, b: int) 
     return ws
 
 
+_fp8_stagings: dict[tuple, torch.Tensor] = {}
+
+
+def _fp8_staging(device: torch.device, stream_id: int, d: int, b: int, s: int) -> torch.Tensor:
+    """Device scratch for the quantised hidden states of the e4m3 path."""
+    key = (device.index, stream_id)
+    need = _lib.query_staging(d, b, s)
+    st = _fp8_stagings.get(key)
+    if st is None or st.numel() < need:
+        st = _fp8_stagings[key] = torch.empty(need, dtype=torch.uint8, device=device)
+    return st
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
     st = _status.get(device.index)
     if st is None:
@@ -117,6 +130,7 @@ def fused_mm_sample(
     return_logprobs: bool = False,  # also return ln p(sampled id) [B, num_samples] from the same pass
     top_k: int | None = None,  # sample among the k largest logits of each row only (1..64)
     top_p: float | None = None,  # with top_k: nucleus cut of the top-k softmax
+    weight_scale: torch.Tensor | None = None,  # [V_local] fp32: `weights` is float8_e4m3fn with one scale per row
 ):
     """Sample ``num_samples`` token ids per hidden-state row from softmax(W h / T).
 
@@ -135,6 +149,10 @@ def fused_mm_sample(
     the pass collects the few candidates at or above a running bound of the k-th largest logit
     and a second small kernel sorts, filters and samples them (``csrc/fmms_topk.cuh``).
 
+    ``weight_scale`` selects e4m3 weights (``weights`` of dtype ``torch.float8_e4m3fn``, one fp32 scale per
+    vocabulary row, e.g. from ``flashsampling_b200.quant.quantize_rows_e4m3``): half the streamed bytes; the
+    hidden states are quantised per row on the way in and the logits are those of the dequantised operands.
+
     With ``tp.size > 1`` every rank passes its own contiguous vocabulary block
     and the same ``hidden_states``, ``temperature`` and ``seed``; all ranks
     return the same global token ids, equal to the single-GPU result.
@@ -149,7 +167,18 @@ def fused_mm_sample(
         raise ValueError(
             f"hidden_states second dimension ({D2}) must match weights second dimension ({D})"
         )
-    if weights.dtype != torch.bfloat16 or hidden_states.dtype != torch.bfloat16:
+    fp8 = weight_scale is not None
+    if fp8:
+        if weights.dtype != torch.float8_e4m3fn or hidden_states.dtype != torch.bfloat16:
+            raise TypeError("with weight_scale, weights must be float8_e4m3fn and hidden_states bfloat16")
+        if weight_scale.shape != (V,) or weight_scale.dtype != torch.float32 or weight_scale.device != weights.device:
+            raise ValueError(f"weight_scale must be fp32 [{V}] on the weights' device")
+        if D % 16 != 0:
+            raise ValueError("e4m3 weights need a hidden size that is a multiple of 16")
+        if kernel == "gemv" or two_stage:
+            raise ValueError("e4m3 weights run on the tensor-core kernel only")
+        weight_scale = weight_scale.contiguous()
+    elif weights.dtype != torch.bfloat16 or hidden_states.dtype != torch.bfloat16:
         raise TypeError("weights and hidden_states must be bfloat16")
     if not weights.is_contiguous():
         raise ValueError("weights must be contiguous")
@@ -246,18 +275,29 @@ def fused_mm_sample(
     fused_tp = tp.size > 1 and getattr(exchange, "fused", False) and B * num_samples <= exchange.max_items \
         and not two_stage and B <= 256  # larger batches run as several launches, then one exchange
     with (_nullcontext if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)):
-        if top_k is not None:
+        if top_k is not None or fp8:
+            # the descriptor form carries what the positional entry points have no argument for
             c = _lib.FmmsCall()
             c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
             (c.W_bf16, c.H_bf16, c.temperature, c.temp_stride, c.V_local, c.D, c.B, c.S, c.seed, c.v_global_offset,
              c.flags, c.ext_noise, c.noise_ld, c.logits_out, c.out_idx, c.out_val, c.workspace, c.workspace_bytes,
              c.status_dev, c.stream) = common
             if return_logprobs:
+                c.flags |= _lib.FLAG_LOGPROB
                 c.out_logprob, c.out_lse = logprobs.data_ptr(), lse.data_ptr()
-            tws = _topk_workspace(dev, stream.cuda_stream, V, B)
-            c.top_k = int(top_k)
-            c.top_p = float(top_p) if top_p is not None else 0.0
-            c.topk_workspace, c.topk_workspace_bytes = tws.data_ptr(), tws.numel()
+            if top_k is not None:
+                tws = _topk_workspace(dev, stream.cuda_stream, V, B)
+                c.top_k = int(top_k)
+                c.top_p = float(top_p) if top_p is not None else 0.0
+                c.topk_workspace, c.topk_workspace_bytes = tws.data_ptr(), tws.numel()
+            if fp8:
+                staging = _fp8_staging(dev, stream.cuda_stream, D, min(B, 256), num_samples)
+                c.flags |= _lib.FLAG_W_FP8
+                c.w_scale = weight_scale.data_ptr()
+                c.staging, c.staging_bytes = staging.data_ptr(), staging.numel()
+            if fused_tp:
+                c.tp_rank, c.tp_world, c.tp_max_items = tp.rank, tp.size, exchange.max_items
+                c.tp_peer_buffers, c.tp_epoch = exchange.ptrs, exchange.next_epoch()
             rc = lib.fmms_run(ctypes.byref(c))
         elif return_logprobs and fused_tp:
             # one launch: winners, their logits and the shards' log-sum-exps all travel in the kernel's exchange
@@ -322,7 +362,7 @@ class SimpleSampler:
     defaults: dict | None = None
 
     def prepare(self) -> "Sampler":
-        if self.weights is not None and self.weights.is_cuda:
+        if self.weights is not None and self.weights.is_cuda and self.weights.dtype == torch.bfloat16:
             return PreparedSampler(self.weights, self.fn, dict(self.defaults or {}))
         return self
 

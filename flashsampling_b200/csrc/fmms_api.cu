@@ -2,6 +2,7 @@
 // checks, kernel selection, TMA descriptor cache and launches.  No torch types, no
 // allocation on the sampling path, no synchronisation.
 #include <cuda.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
@@ -185,6 +186,37 @@ static int get_tensor_map_chunks(const void* ptr, long long rows, long long cols
                                  CUtensorMap* out) {
   return get_tensor_map_3d(ptr, rows, cols, 256, box_rows, chunks, CU_TENSOR_MAP_SWIZZLE_NONE, out);
 }
+
+// ---- fp8 weights: the hidden states are quantised per row on the way in -----------------
+// One CTA per hidden-state row: q = e4m3(h * 448 / amax) (round to nearest even), scale = amax / 448.
+// The same arithmetic, in the same order, as the CPU oracle's quantiser, so both produce the same bytes.
+__global__ void __launch_bounds__(256) quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ h, int D,
+                                                                 unsigned char* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float warp_max[8];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* row = h + (size_t)b * D;
+  float amax = 0.f;
+  for (int i = tid; i < D; i += 256) amax = fmaxf(amax, fabsf(__bfloat162float(row[i])));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, warp_max[w]);
+  amax = fmaxf(amax, 1e-12f);
+  const float inv = 448.0f / amax;
+  if (tid == 0) scale[b] = amax / 448.0f;
+  for (int i = tid; i < D; i += 256)
+    q[(size_t)b * D + i] = (unsigned char)__nv_cvt_float_to_fp8(__bfloat162float(row[i]) * inv, __NV_SATFINITE, __NV_E4M3);
+}
+
+struct Fp8Args {
+  const float* w_scale;  // [V_local]
+  void* staging;         // device memory for the quantised hidden states and their scales
+  size_t staging_bytes;
+};
+static size_t fp8_staging_bytes(int D, int B) { return (((size_t)B * D + 255) & ~(size_t)255) + (size_t)B * 4; }
 
 // ---- GEMV launch ----------------------------------------------------------------
 template <int NB, bool LSE>
@@ -576,7 +608,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
                        size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
-                       float* out_logprob, float* out_lse, int* status_mirror);
+                       float* out_logprob, float* out_lse, int* status_mirror, const Fp8Args* fp8);
 
 struct TpArgs {
   int rank, world, max_items;
@@ -590,7 +622,7 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, float* logits_out,
                        long long* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
                        int* status_dev, void* stream_v, const TpArgs* tpa, float* out_logprob = nullptr,
-                       float* out_lse = nullptr, int* status_mirror = nullptr) {
+                       float* out_lse = nullptr, int* status_mirror = nullptr, const Fp8Args* fp8 = nullptr) {
   g_last_path = FMMS_PATH_NONE;
   if (!W_bf16 || !H_bf16 || !out_idx || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
   const bool greedy = flags & FMMS_FLAG_GREEDY, ext = flags & FMMS_FLAG_EXT_NOISE;
@@ -607,12 +639,19 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
     if (flags & FMMS_FLAG_TWO_STAGE) return FMMS_ERR_UNSUPPORTED;
   }
   if (D % 8 != 0 || ((uintptr_t)W_bf16 & 15) || ((uintptr_t)H_bf16 & 15)) return FMMS_ERR_UNSUPPORTED;
+  if (fp8) {
+    if (!fp8->w_scale || !fp8->staging || ((uintptr_t)fp8->staging & 255) || ((uintptr_t)fp8->w_scale & 15)) return FMMS_ERR_BAD_ARG;
+    if (fp8->staging_bytes < fp8_staging_bytes(D, B > kMaxBatchPerLaunch ? kMaxBatchPerLaunch : B)) return FMMS_ERR_WORKSPACE;
+    if (D % 16 != 0 || (flags & (FMMS_FLAG_FORCE_GEMV | FMMS_FLAG_TWO_STAGE))) return FMMS_ERR_UNSUPPORTED;
+  }
   if (B > kMaxBatchPerLaunch) {
     // Larger batches run as consecutive launches over blocks of 256 rows (each streams W again,
     // as the reference's 64-row tiles do); the noise stays keyed by the caller's row numbers.
     if (tpa) return FMMS_ERR_UNSUPPORTED;
     for (int b0 = 0; b0 < B; b0 += kMaxBatchPerLaunch) {
       const int nb = B - b0 < kMaxBatchPerLaunch ? B - b0 : kMaxBatchPerLaunch;
+      Fp8Args f8{};
+      if (fp8) f8 = Fp8Args{fp8->w_scale, fp8->staging, fp8->staging_bytes};
       const int rc = sample_rows(W_bf16, reinterpret_cast<const __nv_bfloat16*>(H_bf16) + (size_t)b0 * D,
                                  temperature ? temperature + (size_t)b0 * temp_stride : nullptr, temp_stride, V_local,
                                  D, nb, S, seed, v_global_offset, flags,
@@ -621,14 +660,14 @@ static int sample_impl(const void* W_bf16, const void* H_bf16, const float* temp
                                  out_idx + (size_t)b0 * S, out_val ? out_val + (size_t)b0 * S : nullptr, workspace,
                                  workspace_bytes, status_dev, stream_v, nullptr,
                                  out_logprob ? out_logprob + (size_t)b0 * S : nullptr,
-                                 out_lse ? out_lse + b0 : nullptr, status_mirror);
+                                 out_lse ? out_lse + b0 : nullptr, status_mirror, fp8 ? &f8 : nullptr);
       if (rc != FMMS_OK) return rc;
     }
     return FMMS_OK;
   }
   return sample_rows(W_bf16, H_bf16, temperature, temp_stride, V_local, D, B, S, seed, v_global_offset, flags,
                      ext_noise, noise_ld, (long long)B * noise_ld, 0, logits_out, out_idx, out_val, workspace,
-                     workspace_bytes, status_dev, stream_v, tpa, out_logprob, out_lse, status_mirror);
+                     workspace_bytes, status_dev, stream_v, tpa, out_logprob, out_lse, status_mirror, fp8);
 }
 
 static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temperature, int temp_stride,
@@ -636,7 +675,7 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
                        int flags, const float* ext_noise, long long noise_ld, long long noise_s_stride, int b_offset,
                        float* logits_out, long long* out_idx, float* out_val, void* workspace,
                        size_t workspace_bytes, int* status_dev, void* stream_v, const TpArgs* tpa,
-                       float* out_logprob, float* out_lse, int* status_mirror) {
+                       float* out_logprob, float* out_lse, int* status_mirror, const Fp8Args* fp8) {
   const bool greedy = flags & FMMS_FLAG_GREEDY;
   (void)greedy;
   const size_t need = workspace_bytes_for(B, S);  // the least that works; fmms_query_workspace may ask for more
@@ -698,6 +737,22 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
   p.status_mirror = status_mirror;
   p.stamps = g_stamps;
 
+  if (fp8) {
+    // e4m3 weights: quantise the hidden states (per-row scale) into the staging area, then run the tensor-core
+    // kernel on byte matrices that the TMA sees as [rows, D / 2] 16-bit matrices (the same bytes)
+    unsigned char* hq = reinterpret_cast<unsigned char*>(fp8->staging);
+    float* hs = reinterpret_cast<float*>(hq + (((size_t)B * D + 255) & ~(size_t)255));
+    quantize_rows_e4m3_kernel<<<B, 256, 0, stream>>>(p.H, D, hq, hs);
+    if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+    p.flags |= kFlagFp8;
+    p.w_scale = fp8->w_scale;
+    p.h_scale = hs;
+    p.D = D / 2;
+    const int parts8 = launch_umma(*d, W_bf16, hq, p, stream, cap);
+    g_last_path = FMMS_PATH_MMA;
+    if (parts8 <= 0) return parts8 == 0 ? FMMS_ERR_CUDA : -parts8;
+    return FMMS_OK;
+  }
   const bool can_gemv = gemv_eligible(*d, D, B, S);
   bool use_gemv;
   if (flags & FMMS_FLAG_FORCE_GEMV) {
@@ -783,7 +838,7 @@ static StagingLayout staging_layout(int D, int B, int S) {
 
 int fmms_query_staging(int D, int B, int S, size_t* bytes) {
   if (!bytes || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
-  *bytes = staging_layout(D, B, S).total;
+  *bytes = staging_layout(D, B, S).total;  // also covers the quantised hidden states of FMMS_FLAG_W_FP8
   return FMMS_OK;
 }
 
@@ -871,22 +926,38 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
   p.topk.row_fallback = tw + l.rows;
   p.topk.list = reinterpret_cast<unsigned long long*>(tw + l.list);
 
+  const void* h_operand = p.H;
+  if (c.flags & FMMS_FLAG_W_FP8) {
+    // e4m3 weights: quantised hidden states in the staging area, byte matrices seen as [rows, D / 2] (see sample_rows)
+    if (!c.w_scale || !c.staging || ((uintptr_t)c.staging & 255) || c.staging_bytes < fp8_staging_bytes(c.D, nb))
+      return FMMS_ERR_WORKSPACE;
+    if (c.D % 16 != 0) return FMMS_ERR_UNSUPPORTED;
+    unsigned char* hq = reinterpret_cast<unsigned char*>(c.staging);
+    float* hs = reinterpret_cast<float*>(hq + (((size_t)nb * c.D + 255) & ~(size_t)255));
+    quantize_rows_e4m3_kernel<<<nb, 256, 0, stream>>>(p.H, c.D, hq, hs);
+    if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+    p.flags |= kFlagFp8;
+    p.w_scale = c.w_scale;
+    p.h_scale = hs;
+    p.D = c.D / 2;
+    h_operand = hq;
+  }
   // 1. candidate pass (tensor-core kernel, never the CTA-pair variant), 2. one CTA per row finishes
-  int parts = launch_umma(*d, c.W_bf16, p.H, p, stream, 0);
+  int parts = launch_umma(*d, c.W_bf16, h_operand, p, stream, 0);
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
   topk_finish_kernel<<<nb, kTopkFinishThreads, 0, stream>>>(p);
   if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
   // 3. rows whose list overflowed: a conditional greedy pass writes all logits, then exact selection
   if (exact_pass) {
     SampleParams q = p;
-    q.flags = FMMS_FLAG_GREEDY | FMMS_FLAG_RETURN_LOGITS;
+    q.flags = FMMS_FLAG_GREEDY | FMMS_FLAG_RETURN_LOGITS | (p.flags & kFlagFp8);
     q.S = 1;
     q.logits_out = reinterpret_cast<float*>(tw + l.logits);
     q.out_idx = reinterpret_cast<long long*>(tw + l.dummy_idx);
     q.out_val = q.out_logprob = q.out_lse = nullptr;
     q.run_if = p.topk.need_fallback;
     q.topk = TopkArgs{};
-    parts = launch_umma(*d, c.W_bf16, p.H, q, stream, 0);
+    parts = launch_umma(*d, c.W_bf16, h_operand, q, stream, 0);
     if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
     topk_exact_kernel<<<nb, kTopkExactThreads, 0, stream>>>(p, q.logits_out);
   } else {
@@ -944,11 +1015,14 @@ int fmms_run(const fmms_call_t* c) {
   const int kernel_flags = c->flags & ~(FMMS_FLAG_HOST_IO | FMMS_FLAG_NO_SYNC);
   TpArgs tpa{c->tp_rank, c->tp_world, c->tp_max_items, c->tp_peer_buffers, c->tp_epoch, c->tp_wait_limit_ns};
   const TpArgs* tp = c->tp_world > 1 ? &tpa : nullptr;
+  const Fp8Args f8{c->w_scale, c->staging, c->staging_bytes};
+  const bool fp8 = (c->flags & FMMS_FLAG_W_FP8) != 0;
+  if (fp8 && (c->flags & FMMS_FLAG_HOST_IO)) return FMMS_ERR_UNSUPPORTED;
   if (!(c->flags & FMMS_FLAG_HOST_IO))
     return sample_impl(c->W_bf16, c->H_bf16, c->temperature, c->temp_stride, c->V_local, c->D, c->B, c->S, c->seed,
-                       c->v_global_offset, kernel_flags, c->ext_noise, c->noise_ld, c->logits_out, c->out_idx,
-                       c->out_val, c->workspace, c->workspace_bytes, c->status_dev, c->stream, tp, c->out_logprob,
-                       c->out_lse);
+                       c->v_global_offset, kernel_flags & ~FMMS_FLAG_W_FP8, c->ext_noise, c->noise_ld, c->logits_out,
+                       c->out_idx, c->out_val, c->workspace, c->workspace_bytes, c->status_dev, c->stream, tp,
+                       c->out_logprob, c->out_lse, nullptr, fp8 ? &f8 : nullptr);
   // host-memory hidden states, temperatures and results
   if (!c->H_bf16 || !c->out_idx || c->D <= 0 || c->B <= 0 || c->S <= 0 || c->D % 8 != 0) return FMMS_ERR_BAD_ARG;
   const StagingLayout l = staging_layout(c->D, c->B, c->S);

@@ -17,6 +17,7 @@ constexpr int kOk = 0, kErrTimeout = 1, kErrBadArg = 2, kErrUnsupported = 3, kEr
 constexpr int kFlagGreedy = 1, kFlagExtNoise = 2, kFlagReturnLogits = 4, kFlagForceGemv = 8,
               kFlagForceMma = 16, kFlagTwoStage = 32, kFlagSeedDev = 64, kFlagLogprob = 128;
 
+constexpr int kFlagFp8 = 2048;   // W (and the staged hidden states) are e4m3 bytes with per-row scales
 constexpr int kFlagTopk = 1024;  // internal: the launch collects top-k candidates instead of sampling
 
 constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate yet"

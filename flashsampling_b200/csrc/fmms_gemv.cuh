@@ -75,6 +75,9 @@ struct SampleParams {
   unsigned int tp_epoch;
   unsigned long long tp_wait_ns;
   TpPeers tp_peers;
+  // fp8 weights (kFlagFp8): logit = accumulator * w_scale[v] * h_scale[b]
+  const float* w_scale;      // [V] one scale per vocabulary row
+  const float* h_scale;      // [B] one scale per (quantised) hidden-state row
   // top-k / top-p (kFlagTopk): the pass collects candidates, other kernels finish the rows
   TopkArgs topk;
   const unsigned int* run_if;  // optional: the kernel returns at once when this word is zero

@@ -217,6 +217,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
+// The same with e4m3 operands (kind::f8f6f4): 32 values of K per instruction, again 32 bytes of each row.
+__device__ __forceinline__ void umma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle:
 // 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
@@ -230,8 +243,10 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128 (or 64).
-__host__ __device__ inline uint32_t umma_idesc(int n, int m = 128) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// With fp8 the operand formats are e4m3 (format code 0 of kind::f8f6f4) instead of bf16 (code 1 of kind::f16).
+__host__ __device__ inline uint32_t umma_idesc(int n, int m = 128, bool fp8 = false) {
+  const uint32_t fmt = fp8 ? 0u : ((1u << 7) | (1u << 10));
+  return (1u << 4) | fmt | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -274,7 +289,37 @@ struct EpiRow {
   float inv_t;
   bool noisy;     // false for a row whose temperature is <= 0: that row is decoded greedily
   unsigned long long seed;
+  const float* w_scale = nullptr;  // fp8 weights: per-vocabulary-row scales (null: bf16 weights)
+  float h_scale = 1.f;             // fp8 weights: scale of this thread's quantised hidden-state row
 };
+
+// CW accumulator columns of the thread's row, as logits: with fp8 weights the raw sums are multiplied by the
+// scales of the hidden-state row and of each vocabulary row (columns beyond V keep an arbitrary finite factor;
+// no scan uses them).
+template <int CW>
+__device__ __forceinline__ void load_logit_chunk(const SampleParams& p, const EpiRow& e, uint32_t taddr, int vbase,
+                                                 uint32_t (&acc)[CW]) {
+  tmem_ld_chunk<CW>(taddr, acc);
+  if (e.w_scale != nullptr && e.row_ok) {
+    if (vbase + CW <= p.V) {
+      const float4* ws = reinterpret_cast<const float4*>(e.w_scale + vbase);  // vbase is a multiple of 16
+#pragma unroll
+      for (int i = 0; i < CW / 4; ++i) {
+        const float4 w = __ldg(ws + i);
+        acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) * (w.x * e.h_scale));
+        acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) * (w.y * e.h_scale));
+        acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) * (w.z * e.h_scale));
+        acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) * (w.w * e.h_scale));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CW; ++i) {
+        const float w = __ldg(e.w_scale + min(vbase + i, p.V - 1));
+        acc[i] = __float_as_uint(__uint_as_float(acc[i]) * (w * e.h_scale));
+      }
+    }
+  }
+}
 
 // kFlagLogprob: fold the scaled logits of columns [c_begin, c_end) of the accumulator tile into
 // the thread's running log-sum-exp - one maximum and one rescale per CW-column chunk.  A pass of
@@ -285,7 +330,7 @@ __device__ __forceinline__ void lse_tile_columns(const SampleParams& p, const Ep
   const float sc = e.inv_t * kLog2e;  // > 0: the largest logit gives the largest scaled logit
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
-    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
+    load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
     if (e.row_ok) {
       const int n_ok = min(c_end - c, p.V - (v0 + c));  // valid columns of this chunk
       float mx = -INFINITY;
@@ -315,7 +360,7 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
                                                   int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
-    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
+    load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
     if (e.row_ok) {
       const int vbase = v0 + c;
       if (e.ret_logits && s == 0) {
@@ -399,7 +444,7 @@ __device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const E
                                                   int c_end, int v0, float pivot, bool append, float& tmax) {
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
-    tmem_ld_chunk<CW>(t_addr + (uint32_t)c, acc);
+    load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
     if (e.row_ok) {
       const int vbase = v0 + c;
 #pragma unroll
@@ -578,6 +623,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       bool ok = true;
       TileWalk walk(units_total, n_tiles);
       const uint32_t a_shift = (uint32_t)(16384 / R);  // bytes by which each further replica's A operand starts earlier
+      const bool fp8 = (p.flags & kFlagFp8) != 0;
       for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
         const TileInfo ti = walk.next();
         const int NT = ti.nt;
@@ -609,16 +655,23 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
                 if (ce == cb) continue;
                 const uint64_t adesc = umma_smem_desc(a_slab - (uint32_t)r * a_shift);
                 const uint64_t bdesc = umma_smem_desc(w_slab + (uint32_t)(cb * 128));
-                const uint32_t idesc = umma_idesc(ce - cb, m64 ? 64 : 128);
+                const uint32_t idesc = umma_idesc(ce - cb, m64 ? 64 : 128, fp8);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap + cb);
+                if (fp8) {
 #pragma unroll
-                for (int k = 0; k < kUmmaBK / 16; ++k)
-                  umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                            (kb | sl | k) != 0 ? 1u : 0u);
+                  for (int k = 0; k < kUmmaBK / 16; ++k)
+                    umma_e4m3(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (kb | sl | k) != 0 ? 1u : 0u);
+                } else {
+#pragma unroll
+                  for (int k = 0; k < kUmmaBK / 16; ++k)
+                    umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (kb | sl | k) != 0 ? 1u : 0u);
+                }
               }
             } else {
               const uint64_t bdesc = umma_smem_desc(w_slab);
-              const uint32_t idesc = umma_idesc(NT);
+              const uint32_t idesc = umma_idesc(NT, 128, fp8);
 #pragma unroll
               for (int m = 0; m < MT; ++m) {
                 const uint64_t adesc =
@@ -626,9 +679,13 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
                 const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
 #pragma unroll
                 for (int k = 0; k < kUmmaBK / 16; ++k) {
-                  // advance both descriptors by 16 bf16 = 32 bytes inside the swizzled row
-                  umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                            (kb | sl | k) != 0 ? 1u : 0u);
+                  // advance both descriptors by 16 bf16 (32 e4m3) = 32 bytes inside the swizzled row
+                  if (fp8)
+                    umma_e4m3(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (kb | sl | k) != 0 ? 1u : 0u);
+                  else
+                    umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (kb | sl | k) != 0 ? 1u : 0u);
                 }
               }
             }
@@ -667,7 +724,11 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       noisy = temp > 0.f;  // temperature <= 0 selects greedy decoding for this row
       invT = noisy ? 1.0f / temp : 1.0f;
     }
-    const EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy, resolve_seed(p.seed, p.flags)};
+    EpiRow row{b, row_ok, greedy, ext, ret_logits, quad_aligned, invT, noisy, resolve_seed(p.seed, p.flags)};
+    if (p.flags & kFlagFp8) {
+      row.w_scale = p.w_scale;
+      row.h_scale = row_ok ? p.h_scale[b] : 1.f;
+    }
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.cand_rows);
     const bool narrow = (R == 4);  // four replicas leave ~50 columns per quadrant: deal them out in 16-column chunks

@@ -58,6 +58,8 @@ extern "C" {
                                       out_logprob / out_lse are HOST pointers (pinned memory recommended); the
                                       call copies them through the caller's device `staging` buffer           */
 #define FMMS_FLAG_NO_SYNC 512      /* with FMMS_FLAG_HOST_IO: do not wait for the stream before returning   */
+#define FMMS_FLAG_W_FP8 2048       /* fmms_run() only: W_bf16 points to e4m3 bytes [V_local, D] with one fp32
+                                      scale per row in `w_scale` (weight = byte value * scale); see fmms_call_t */
 
 /* kernel paths reported by fmms_last_path() */
 #define FMMS_PATH_NONE 0
@@ -240,6 +242,14 @@ typedef struct fmms_call {
   float top_p;              /* nucleus mass in (0, 1); any other value: top-k only */
   void* topk_workspace;     /* device memory, 256-byte aligned, ZERO before its first use */
   size_t topk_workspace_bytes;
+  /* FMMS_FLAG_W_FP8: e4m3 weights.  `W_bf16` then holds V_local x D bytes (D % 16 == 0), `w_scale` one fp32
+   * scale per vocabulary row (16-byte aligned); the call quantises the bf16 hidden states per row to e4m3
+   * (scale = max|h| / 448) into `staging` (device memory of fmms_query_staging() bytes; no other use of it in
+   * this mode), multiplies with tcgen05.mma kind::f8f6f4 and applies both scales to the fp32 sums before the
+   * temperature.  Half the bytes of the bf16 stream.  Works with tensor parallelism, log-probabilities and
+   * top-k; not with FMMS_FLAG_HOST_IO, FMMS_FLAG_TWO_STAGE or the small-batch kernel.  The reference has no
+   * counterpart (it names quantised LM heads as future work, findings/cutlass-fmms-kernel-plan.md:1076-1077). */
+  const float* w_scale;
 } fmms_call_t;
 
 int fmms_run(const fmms_call_t* call);

@@ -307,6 +307,40 @@ def topk_topp_sample(logits, temperature, top_k, top_p, num_samples: int, seed: 
     return ids.gather(dim=-1, index=picks)
 
 
+# ---------------------------------------------------------------------------
+# e4m3 weights: what the fp8 kernels compute, restated (no reference counterpart:
+# the reference leaves quantised LM heads to future work,
+# findings/cutlass-fmms-kernel-plan.md:1076-1077)
+# ---------------------------------------------------------------------------
+
+
+def e4m3_round_nearest_even(y: torch.Tensor) -> torch.Tensor:
+    """Nearest e4m3 value (1 sign, 4 exponent, 3 mantissa bits, bias 7, no infinities, largest finite value
+    448), ties to the even mantissa, saturating: what the CUDA conversion does."""
+    a = y.double().abs()
+    e = torch.floor(torch.log2(a.clamp_min(2.0 ** -40))).clamp_min(-6.0)
+    step = torch.pow(torch.tensor(2.0, dtype=torch.float64), e - 3.0)
+    q = (torch.round(a / step) * step).clamp_max(448.0)
+    return torch.copysign(q, y.double()).float()
+
+
+def quantize_rows_e4m3(x: torch.Tensor):
+    """Per-row e4m3 quantisation: ``q = e4m3(x * (448 / amax))`` (round to nearest even),
+    ``scale = amax / 448``; returns ``(q float8_e4m3fn, scale fp32 [rows])``."""
+    xf = x.float()
+    amax = xf.abs().amax(dim=1).clamp_min(1e-12)
+    inv = torch.full_like(amax, 448.0) / amax  # true division (`scalar / tensor` would be reciprocal * scalar)
+    return e4m3_round_nearest_even(xf * inv[:, None]).to(torch.float8_e4m3fn), amax / torch.full_like(amax, 448.0)
+
+
+def quantized_logits(w_q: torch.Tensor, w_scale: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
+    """fp32 logits of the e4m3 path: both operands dequantised (the products of two e4m3 values are exact
+    in fp32), hidden states quantised per row exactly as the kernels do on the way in."""
+    h_q, h_scale = quantize_rows_e4m3(hidden_states)
+    acc = h_q.float() @ w_q.float().T
+    return acc * (w_scale.float()[None, :] * h_scale[:, None])
+
+
 def weight_read_time_us(vocab: int, hidden: int, tb_per_s: float = 8.0) -> float:
     """Pure weight-streaming time of a [vocab, hidden] bf16 matrix in microseconds."""
     return 2.0 * vocab * hidden / (tb_per_s * 1e12) * 1e6
