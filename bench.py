@@ -315,6 +315,22 @@ def run_b200(args):
             topk_step()
             tk, _ = time_steps(topk_step, max(20, steps // 4), 5, sweep_read, barrier)
             pair["topk_ms"] = tk
+        if with_e2e and world == 1:
+            # the same step on e4m3 weights with per-row scales (half the streamed bytes)
+            from flashsampling_b200.quant import quantize_rows_e4m3
+
+            wq, wscale = quantize_rows_e4m3(w)
+            wqs = [wq] + [wq.clone() for _ in range(min(n_copies, 4) - 1)]
+
+            def fp8_step():
+                seed[0] += S
+                turn[0] += 1
+                return fs.fused_mm_sample(wqs[turn[0] % len(wqs)], h, S, t, seed=seed[0], weight_scale=wscale)
+
+            fp8_step()
+            f8, _ = time_steps(fp8_step, max(20, steps // 4), 5, sweep_read, barrier)
+            pair["fp8_ms"] = f8
+            del wq, wqs
         if with_e2e:
             h_host = h.cpu().pin_memory()
             t_host = t.cpu().reshape(-1).pin_memory()
@@ -488,6 +504,14 @@ def run_b200(args):
             "note": "the step with top_k=50, top_p=0.9 (candidate pass + per-row finish kernel + the two conditional "
                     "launches of the exact pass, which return at once), per-call CUDA events like `value`",
         }} if "topk_ms" in main else {}),
+        **({"fp8_weights": {
+            "us": round(statistics.median(main["fp8_ms"]) * 1e3, 3),
+            "algorithmic_bytes_per_launch": V * D + 2 * B * D + 8 * B * S + 4 * V,
+            "hbm_gbs": round((V * D + 2 * B * D + 8 * B * S + 4 * V) / (statistics.median(main["fp8_ms"]) * 1e-3) / 1e9, 1),
+            "note": "the step on e4m3 weights with one fp32 scale per vocabulary row (weight_scale=): per-row "
+                    "quantisation kernel for the hidden states + tcgen05.mma kind::f8f6f4 sampling kernel, per-call "
+                    "CUDA events like `value`; the distribution is that of the quantised head",
+        }} if "fp8_ms" in main else {}),
         "env": {"gpu": torch.cuda.get_device_name(device), "torch": torch.__version__, "cuda": torch.version.cuda},
         **({"tp_ids_equal_unsharded": main["tp_equal"]} if main["tp_equal"] is not None else {}),
         "gpu_launches": args.steps,  # one fused kernel per step (matmul + noise + argmax + cross-CTA/cross-rank reduction)
@@ -700,10 +724,15 @@ def run_once(args):
     wl = WORKLOADS[args.workload]
     w, h, t = make_inputs(wl, args.batch, 0, 1, device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    w_scale = None
+    if args.fp8:
+        from flashsampling_b200.quant import quantize_rows_e4m3
+
+        w, w_scale = quantize_rows_e4m3(w)
     for i in range(5):
         _lib.load().fmms_l2_sweep(flush.data_ptr(), flush.numel(), torch.cuda.current_stream().cuda_stream)
         fs.fused_mm_sample(w, h, wl["S"], t, seed=i, kernel=args.kernel, top_k=args.top_k or None,
-                           top_p=(args.top_p or None) if args.top_k else None)
+                           top_p=(args.top_p or None) if args.top_k else None, weight_scale=w_scale)
     torch.cuda.synchronize()
     fs.check_status()
     print(json.dumps({"once": True, "workload": args.workload, "batch": args.batch, "kernel": fs.last_path(),
@@ -789,6 +818,7 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--once", action="store_true", help="five calls of one configuration, for profilers")
     ap.add_argument("--kernel", default=None, choices=["gemv", "mma"], help="--once: force a kernel")
+    ap.add_argument("--fp8", action="store_true", help="--once: e4m3 weights with per-row scales")
     ap.add_argument("--top-k", type=int, default=0, help="--once: sample with top-k (0 = off); the benchmark's top-k leg uses 50")
     ap.add_argument("--top-p", type=float, default=0.0, help="--once: nucleus mass used with --top-k")
     ap.add_argument("--reference-triton", action=argparse.BooleanOptionalAction, default=True,

@@ -438,15 +438,12 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     }
   }
 
-  int it = 0;
+  int st = 0;          // ring slot of the next pipeline step and the parity of its "full" barrier (counted, not divided)
+  uint32_t phase = 0;
   for (;;) {
     // the first ring slot of a group tells which group it is
-    {
-      const int st = it % stages;
-      const uint32_t n = (uint32_t)(it / stages);
-      if (!mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev)) break;
-    }
-    const int g = stage_group[it % stages];
+    if (!mbar_wait(&full_bar[st], phase, abort_flag, p.status_dev)) break;
+    const int g = stage_group[st];
     if (g < 0) break;
     float2 acc[kGemvRowsPerWarp][NB];
 #pragma unroll
@@ -454,10 +451,8 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
 #pragma unroll
       for (int b = 0; b < NB; ++b) acc[r][b] = make_float2(0.f, 0.f);
 
-    for (int kc = 0; kc < KC; ++kc, ++it) {
-      const int st = it % stages;
-      const uint32_t n = (uint32_t)(it / stages);
-      mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev);
+    for (int kc = 0; kc < KC; ++kc) {
+      mbar_wait(&full_bar[st], phase, abort_flag, p.status_dev);
 
       for (int c = 0; c < CK; ++c) {
         float2 hreg[NB][4];
@@ -488,6 +483,10 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[st]);
+      if (++st == stages) {
+        st = 0;
+        phase ^= 1u;
+      }
     }
 
     // warp-wide sums: every lane ends up with all 4 * NB logits of the warp's rows

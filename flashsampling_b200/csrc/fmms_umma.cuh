@@ -577,6 +577,8 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       }
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
       int it = 0;
+      int st = 0;          // ring slot of the next K step, and the parity of its "empty" barrier
+      uint32_t phase = 1;
       bool ok = true;
       TileWalk walk(units_total, n_tiles);
       const bool flat = (SK == 1);  // one slab per stage: 2-D maps
@@ -588,9 +590,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         const CUtensorMap* wm = (NT == q_units * 16) ? &w_map_q : &w_map_q1;
         const size_t h_off = (size_t)SK * NT * 128;   // hidden-state slabs follow the W slabs
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int st = it % stages;
-          const uint32_t n = (uint32_t)(it / stages);
-          if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) {
+          if (!mbar_wait(&empty_bar[st], phase, abort_flag, p.status_dev)) {
             ok = false;
             break;
           }
@@ -607,6 +607,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
               else tma_load_3d_hint(dst, &h_map, 0, m * 128, kb * SK, &full_bar[st], pol);
             }
           }
+          if (++st == stages) {
+            st = 0;
+            phase ^= 1u;
+          }
         }
       }
       if (*abort_flag) {
@@ -618,81 +622,102 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
   } else if (warp == mma_warp) {
     // ------------------------------ MMA issuer --------------------------------
+    // One thread feeds the tensor core, and a K step's MMA takes about as long as the HBM needs for that step's
+    // bytes: the loop between two tcgen05.mma is kept free of divisions and repeated branches (per-tile
+    // constants are hoisted, ring slot and phase are counted, the operand kind is decided once per K step).
     if (lane == 0) {
-      int it = 0;
       bool ok = true;
       TileWalk walk(units_total, n_tiles);
       const uint32_t a_shift = (uint32_t)(16384 / R);  // bytes by which each further replica's A operand starts earlier
       const bool fp8 = (p.flags & kFlagFp8) != 0;
-      for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
+      const uint32_t smem0 = smem_u32(smem);
+      int st = 0;            // ring slot of the next K step
+      uint32_t phase = 0;    // its parity
+      bool first = true;
+      int j = 0;             // accumulator buffer of the next tile
+      uint32_t acc_phase = 0;
+      for (int t = 0; t < n_tiles && ok; ++t) {
         const TileInfo ti = walk.next();
         const int NT = ti.nt;
         if (NT == 0) continue;
         const uint32_t h_off = (uint32_t)(SK * NT * 128);
-        const int j = ta % acc_stages;
-        const uint32_t un = (uint32_t)(ta / acc_stages);
-        ++ta;
-        if (!mbar_wait(&acc_empty[j], (un & 1u) ^ 1u, abort_flag, p.status_dev)) break;
+        const uint32_t w_pitch = (uint32_t)(NT * 128);  // TMA packs the slabs of a box back to back: the pitch follows the tile height
+        // the column ranges (and instruction descriptors) of the replicas; R = 1: the whole tile
+        int cb[4] = {0, 0, 0, 0};
+        uint32_t idesc[4] = {0, 0, 0, 0};
+        for (int r = 0; r < R; ++r) {
+          int ce;
+          replica_columns(NT, R, r, cb[r], ce);
+          idesc[r] = ce > cb[r] ? umma_idesc(ce - cb[r], m64 ? 64 : 128, fp8) : 0u;
+        }
+        const uint32_t idesc_full = umma_idesc(NT, 128, fp8);
+        if (!mbar_wait(&acc_empty[j], acc_phase ^ 1u, abort_flag, p.status_dev)) break;
         tc_fence_after();
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int st = it % stages;
-          const uint32_t n = (uint32_t)(it / stages);
-          if (!mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev)) {
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full_bar[st], phase, abort_flag, p.status_dev)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (it == 0) stamp(p, 2);
-          const uint32_t sw = smem_u32(smem + st * stage_bytes);
+          if (first) {
+            stamp(p, 2);
+            first = false;
+          }
+          const uint32_t sw = smem0 + (uint32_t)st * (uint32_t)stage_bytes;
           for (int sl = 0; sl < SK; ++sl) {
-            // TMA packs the slabs of a box back to back: the slab pitch follows the tile height
-            const uint32_t w_slab = sw + (uint32_t)(sl * NT * 128);
+            const uint32_t w_slab = sw + (uint32_t)sl * w_pitch;
+            const uint32_t acc0 = (kb | sl) != 0 ? 1u : 0u;
             if (MT == 1) {
               const uint32_t a_slab = sw + h_off + (uint32_t)(sl * h_slab_bytes);
               for (int r = 0; r < R; ++r) {
-                int cb, ce;
-                replica_columns(NT, R, r, cb, ce);
-                if (ce == cb) continue;
+                if (idesc[r] == 0u) continue;
                 const uint64_t adesc = umma_smem_desc(a_slab - (uint32_t)r * a_shift);
-                const uint64_t bdesc = umma_smem_desc(w_slab + (uint32_t)(cb * 128));
-                const uint32_t idesc = umma_idesc(ce - cb, m64 ? 64 : 128, fp8);
-                const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap + cb);
+                const uint64_t bdesc = umma_smem_desc(w_slab + (uint32_t)(cb[r] * 128));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap + cb[r]);
+                // advance both descriptors by 16 bf16 (32 e4m3) = 32 bytes inside the swizzled row
                 if (fp8) {
-#pragma unroll
-                  for (int k = 0; k < kUmmaBK / 16; ++k)
-                    umma_e4m3(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                              (kb | sl | k) != 0 ? 1u : 0u);
+                  umma_e4m3(d_tmem, adesc, bdesc, idesc[r], acc0);
+                  umma_e4m3(d_tmem, adesc + 2, bdesc + 2, idesc[r], 1u);
+                  umma_e4m3(d_tmem, adesc + 4, bdesc + 4, idesc[r], 1u);
+                  umma_e4m3(d_tmem, adesc + 6, bdesc + 6, idesc[r], 1u);
                 } else {
-#pragma unroll
-                  for (int k = 0; k < kUmmaBK / 16; ++k)
-                    umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                              (kb | sl | k) != 0 ? 1u : 0u);
+                  umma_bf16(d_tmem, adesc, bdesc, idesc[r], acc0);
+                  umma_bf16(d_tmem, adesc + 2, bdesc + 2, idesc[r], 1u);
+                  umma_bf16(d_tmem, adesc + 4, bdesc + 4, idesc[r], 1u);
+                  umma_bf16(d_tmem, adesc + 6, bdesc + 6, idesc[r], 1u);
                 }
               }
             } else {
               const uint64_t bdesc = umma_smem_desc(w_slab);
-              const uint32_t idesc = umma_idesc(NT, 128, fp8);
 #pragma unroll
               for (int m = 0; m < MT; ++m) {
-                const uint64_t adesc =
-                    umma_smem_desc(sw + h_off + (uint32_t)((m * SK + sl) * h_slab_bytes));
+                const uint64_t adesc = umma_smem_desc(sw + h_off + (uint32_t)((m * SK + sl) * h_slab_bytes));
                 const uint32_t d_tmem = tmem_base + (uint32_t)((j * MT + m) * nt_cap);
-#pragma unroll
-                for (int k = 0; k < kUmmaBK / 16; ++k) {
-                  // advance both descriptors by 16 bf16 (32 e4m3) = 32 bytes inside the swizzled row
-                  if (fp8)
-                    umma_e4m3(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                              (kb | sl | k) != 0 ? 1u : 0u);
-                  else
-                    umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                              (kb | sl | k) != 0 ? 1u : 0u);
+                if (fp8) {
+                  umma_e4m3(d_tmem, adesc, bdesc, idesc_full, acc0);
+                  umma_e4m3(d_tmem, adesc + 2, bdesc + 2, idesc_full, 1u);
+                  umma_e4m3(d_tmem, adesc + 4, bdesc + 4, idesc_full, 1u);
+                  umma_e4m3(d_tmem, adesc + 6, bdesc + 6, idesc_full, 1u);
+                } else {
+                  umma_bf16(d_tmem, adesc, bdesc, idesc_full, acc0);
+                  umma_bf16(d_tmem, adesc + 2, bdesc + 2, idesc_full, 1u);
+                  umma_bf16(d_tmem, adesc + 4, bdesc + 4, idesc_full, 1u);
+                  umma_bf16(d_tmem, adesc + 6, bdesc + 6, idesc_full, 1u);
                 }
               }
             }
           }
           umma_commit(&empty_bar[st]);  // stage reusable once these MMAs have read it
+          if (++st == stages) {
+            st = 0;
+            phase ^= 1u;
+          }
         }
         if (ok) umma_commit(&acc_full[j]);  // accumulator complete
+        if (++j == acc_stages) {
+          j = 0;
+          acc_phase ^= 1u;
+        }
       }
       stamp(p, 3);
     }

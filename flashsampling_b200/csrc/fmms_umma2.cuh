@@ -213,7 +213,8 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
         prefetch_tmap(&h_map);
       }
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
-      int it = 0;
+      int st = 0;          // ring slot of the next K step and the parity of its "empty" barrier (no divisions here)
+      uint32_t phase = 1;
       bool ok = true;
       PairWalk walk(units_total, n_tiles);
       for (int t = 0; t < n_tiles && ok; ++t) {
@@ -223,10 +224,8 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
         const int half = NT / 2;
         const uint32_t tx = (uint32_t)SK * (is_w ? (uint32_t)half * 128u : (uint32_t)h_slab_bytes);
         const CUtensorMap* wm = (NT == q_units * kPairUnitRows) ? &w_map_q : &w_map_q1;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int st = it % stages;
-          const uint32_t n = (uint32_t)(it / stages);
-          if (!mbar_wait(&empty_bar[st], (n & 1u) ^ 1u, abort_flag, p.status_dev)) {
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&empty_bar[st], phase, abort_flag, p.status_dev)) {
             ok = false;
             break;
           }
@@ -237,51 +236,66 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
             tma_pair_load_3d(sw, wm, 0, v0 + (int)rank * half, kb * SK, bar, pol);
           else
             tma_pair_load_3d(sw + w_tile_bytes, &h_map, 0, (int)rank * 128, kb * SK, bar, pol);
+          if (++st == stages) {
+            st = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) --------------------------
     if (leader && lane == 0) {
-      int it = 0;
+      // the loop between two tcgen05.mma is kept free of divisions: ring slot, parity and accumulator buffer are counted
+      int st = 0, j = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool first = true;
       bool ok = true;
+      const uint32_t smem0 = smem_u32(smem);
       PairWalk walk(units_total, n_tiles);
-      for (int t = 0, ta = 0; t < n_tiles && ok; ++t) {
+      for (int t = 0; t < n_tiles && ok; ++t) {
         int v0, NT;
         walk.next(v0, NT);
         if (NT == 0) continue;
         const uint32_t idesc = umma_pair_idesc(NT);
-        const int j = ta % acc_stages;
-        const uint32_t un = (uint32_t)(ta / acc_stages);
-        ++ta;
-        if (!mbar_wait(&acc_empty[j], (un & 1u) ^ 1u, abort_flag, p.status_dev)) break;
+        const uint32_t w_pitch = (uint32_t)((NT / 2) * 128);
+        if (!mbar_wait(&acc_empty[j], acc_phase ^ 1u, abort_flag, p.status_dev)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(j * nt_cap);
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int st = it % stages;
-          const uint32_t n = (uint32_t)(it / stages);
-          if (!mbar_wait(&full_bar[st], n & 1u, abort_flag, p.status_dev)) {
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full_bar[st], phase, abort_flag, p.status_dev)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (it == 0) stamp(p, 2);
-          const uint32_t sw = smem_u32(smem + st * stage_bytes);
+          if (first) {
+            stamp(p, 2);
+            first = false;
+          }
+          const uint32_t sw = smem0 + (uint32_t)st * (uint32_t)stage_bytes;
           for (int sl = 0; sl < SK; ++sl) {
-            const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)(sl * (NT / 2) * 128));
+            const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)sl * w_pitch);
             const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + sl * h_slab_bytes));
-#pragma unroll
-            for (int k = 0; k < kUmmaBK / 16; ++k)
-              umma_pair_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                             (kb | sl | k) != 0 ? 1u : 0u);
+            umma_pair_bf16(d_tmem, adesc, bdesc, idesc, (kb | sl) != 0 ? 1u : 0u);
+            umma_pair_bf16(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+            umma_pair_bf16(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+            umma_pair_bf16(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           umma_pair_commit(smem_u32(&empty_bar[st]));
           umma_pair_commit(mapa_shared(smem_u32(&empty_bar[st]), 1));
+          if (++st == stages) {
+            st = 0;
+            phase ^= 1u;
+          }
         }
         if (ok) {
           umma_pair_commit(smem_u32(&acc_full[j]));
           umma_pair_commit(mapa_shared(smem_u32(&acc_full[j]), 1));
+        }
+        if (++j == acc_stages) {
+          j = 0;
+          acc_phase ^= 1u;
         }
       }
       stamp(p, 3);

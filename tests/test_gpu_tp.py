@@ -82,6 +82,19 @@ def _tp_worker(world):
     assert torch.equal(ids, full_ids), (tp.rank, (ids != full_ids).sum().item())
     assert float((lp - full_lp).abs().max()) < 1e-3
     fs.check_status()
+    # e4m3 weights with per-row scales, sharded: the ids of the unsharded e4m3 draw
+    from flashsampling_b200.quant import quantize_rows_e4m3
+
+    V, D, B, S = 16384 - 16384 % world, 256, 48, 1
+    w, h = gaussian_head(V, D, B, 0.08, seed=21)
+    wq, wsc = quantize_rows_e4m3(w)
+    hd = h.to(dev)
+    full = fs.fused_mm_sample(wq.to(dev), hd, S, t, seed=11, weight_scale=wsc.to(dev))
+    lo, hi = tp.shard_rows(V)
+    got = fs.fused_mm_sample(wq[lo:hi].contiguous().to(dev), hd, S, t, seed=11, tp=tp,
+                             weight_scale=wsc[lo:hi].contiguous().to(dev))
+    assert torch.equal(got, full), (tp.rank, (got != full).sum().item())
+    fs.check_status()
     # the reference's distributed protocol: chi-square per rank on sharded ramps (testing.py:264-275)
     for V, nh in ((256, 2), (512, 1)):
         assert_sampling_distribution("fused-triton", V, nh, tp=tp)
