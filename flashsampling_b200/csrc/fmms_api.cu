@@ -193,6 +193,7 @@ static int get_tensor_map_chunks(const void* ptr, long long rows, long long cols
 __global__ void __launch_bounds__(256) quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ h, int D,
                                                                  unsigned char* __restrict__ q, float* __restrict__ scale) {
   __shared__ float warp_max[8];
+  griddep_launch_dependents();  // the sampling kernel behind this one may start its weight stream now
   const int b = blockIdx.x, tid = threadIdx.x;
   const __nv_bfloat16* row = h + (size_t)b * D;
   float amax = 0.f;
@@ -218,6 +219,31 @@ struct Fp8Args {
 };
 static size_t fp8_staging_bytes(int D, int B) { return (((size_t)B * D + 255) & ~(size_t)255) + (size_t)B * 4; }
 
+// ---- launches ---------------------------------------------------------------------
+// g_overlap_next: the next sampling kernel may start while the kernel enqueued just before it (the hidden-state
+// quantiser or the host-buffer gather, both of which release their dependents at once) still runs; the sampling
+// kernels wait (griddepcontrol.wait) before they touch anything that kernel writes.  Consumed by one launch.
+static thread_local bool g_overlap_next = false;
+
+template <class... KArgs, class... Args>
+static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (g_overlap_next) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_overlap_next = false;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- GEMV launch ----------------------------------------------------------------
 template <int NB, bool LSE>
 static int launch_gemv_nb_lse(DeviceInfo& d, const CUtensorMap& map, SampleParams& p, int grid, size_t smem,
@@ -228,8 +254,7 @@ static int launch_gemv_nb_lse(DeviceInfo& d, const CUtensorMap& map, SampleParam
       return kErrCuda;
     d.gemv_attr[LSE][NB] = true;
   }
-  gemv_sample_kernel<NB, LSE><<<grid, kGemvThreads, smem, stream>>>(map, p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+  return launch_kernel(gemv_sample_kernel<NB, LSE>, grid, kGemvThreads, smem, stream, map, p) == cudaSuccess ? kOk : kErrCuda;
 }
 
 // The kernels that also accumulate the log-sum-exp (kFlagLogprob) are separate instantiations,
@@ -334,9 +359,10 @@ static int launch_umma_variant(DeviceInfo& d, const UmmaMaps& mp, SampleParams& 
       return kErrCuda;
     attr_set = true;
   }
-  umma_sample_kernel<MT, LSE, TOPK><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(
-      mp.wq, mp.wq1, mp.hm, p, pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies, pl.m_rows);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+  return launch_kernel(umma_sample_kernel<MT, LSE, TOPK>, pl.grid, kUmmaThreads, pl.smem, stream, mp.wq, mp.wq1, mp.hm, p,
+                       pl.nt_cap, pl.units_total, pl.q_units, pl.h_rows, pl.slabs, pl.copies, pl.m_rows) == cudaSuccess
+             ? kOk
+             : kErrCuda;
 }
 
 // The kernels that also accumulate the log-sum-exp (kFlagLogprob) or collect top-k candidates
@@ -458,13 +484,12 @@ static int launch_umma_pair(DeviceInfo& d, const void* W, const void* H, SampleP
   p.tile_rows = pl.q_units * kPairUnitRows;
   p.tiles_per_cta = pl.tiles_per_pair;
   p.lse_parts = pl.grid / 2;
-  if (lse)
-    umma_pair_sample_kernel<true><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total,
-                                                                              pl.q_units, pl.slabs);
-  else
-    umma_pair_sample_kernel<false><<<pl.grid, kUmmaThreads, pl.smem, stream>>>(wq, wq1, hm, p, pl.units_total,
-                                                                               pl.q_units, pl.slabs);
-  if (cudaGetLastError() != cudaSuccess) return -kErrCuda;
+  const cudaError_t err =
+      lse ? launch_kernel(umma_pair_sample_kernel<true>, pl.grid, kUmmaThreads, pl.smem, stream, wq, wq1, hm, p,
+                          pl.units_total, pl.q_units, pl.slabs)
+          : launch_kernel(umma_pair_sample_kernel<false>, pl.grid, kUmmaThreads, pl.smem, stream, wq, wq1, hm, p,
+                          pl.units_total, pl.q_units, pl.slabs);
+  if (err != cudaSuccess) return -kErrCuda;
   return pl.grid * kUmmaEpiGroups;
 }
 
@@ -748,7 +773,9 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
     p.w_scale = fp8->w_scale;
     p.h_scale = hs;
     p.D = D / 2;
+    g_overlap_next = true;  // the weight stream starts while the quantiser runs
     const int parts8 = launch_umma(*d, W_bf16, hq, p, stream, cap);
+    g_overlap_next = false;
     g_last_path = FMMS_PATH_MMA;
     if (parts8 <= 0) return parts8 == 0 ? FMMS_ERR_CUDA : -parts8;
     return FMMS_OK;
@@ -941,9 +968,11 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
     p.h_scale = hs;
     p.D = c.D / 2;
     h_operand = hq;
+    g_overlap_next = true;
   }
   // 1. candidate pass (tensor-core kernel, never the CTA-pair variant), 2. one CTA per row finishes
   int parts = launch_umma(*d, c.W_bf16, h_operand, p, stream, 0);
+  g_overlap_next = false;
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
   topk_finish_kernel<<<nb, kTopkFinishThreads, 0, stream>>>(p);
   if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
@@ -1004,6 +1033,7 @@ static void* host_ptr_on_device(const void* host) {
 // and the compute engine, several microseconds, before the sampling kernel may start).
 static __global__ void stage_host_inputs_kernel(const uint4* __restrict__ h_src, uint4* __restrict__ h_dst, size_t n16,
                                          const float* __restrict__ t_src, float* __restrict__ t_dst, int nt) {
+  griddep_launch_dependents();  // the sampling kernel behind this one may start its weight stream now
   const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = i0; i < n16; i += stride) h_dst[i] = h_src[i];
   for (size_t i = i0; i < (size_t)nt; i += stride) t_dst[i] = t_src[i];
@@ -1048,6 +1078,7 @@ int fmms_run(const fmms_call_t* c) {
                                                          reinterpret_cast<const float*>(t_map),
                                                          reinterpret_cast<float*>(st + l.t), nt);
     if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+    g_overlap_next = true;  // the sampling kernel's weight stream starts while the gather runs
   } else {
     if (cudaMemcpyAsync(st + l.h, c->H_bf16, h_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return FMMS_ERR_CUDA;
     if (nt && cudaMemcpyAsync(st + l.t, c->temperature, (size_t)nt * 4, cudaMemcpyHostToDevice, stream) != cudaSuccess)
@@ -1064,6 +1095,9 @@ int fmms_run(const fmms_call_t* c) {
   const bool direct = idx_map && (!c->out_val || val_map) && (!c->out_logprob || lp_map) && (!c->out_lse || lse_map) &&
                       (!(c->status_host && c->status_dev) || status_map);
   int rc;
+  struct ClearOverlap {
+    ~ClearOverlap() { g_overlap_next = false; }
+  } clear_overlap;  // whatever path the call takes from here
   if (direct) {
     rc = sample_impl(c->W_bf16, st + l.h, temp_dev, c->temp_stride, c->V_local, c->D, c->B, c->S, c->seed,
                      c->v_global_offset, kernel_flags, c->ext_noise, c->noise_ld, c->logits_out, idx_map, val_map,

@@ -321,6 +321,13 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   return p;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may start
+// while the kernel before it on the stream still runs; griddep_wait() blocks until that kernel has completed
+// and its writes are visible (it returns at once in a kernel launched the ordinary way).  The earlier kernel
+// calls griddep_launch_dependents() to let the next one start.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

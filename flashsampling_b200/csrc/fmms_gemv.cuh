@@ -339,7 +339,8 @@ gemv_sample_kernel(const __grid_constant__ CUtensorMap w_map, const SampleParams
     fence_mbar_init();
     stamp(p, 0);
   }
-  // hidden states -> shared memory, zero padded to [NB][Dpad]
+  // hidden states -> shared memory, zero padded to [NB][Dpad] (they may come from the kernel just before this one)
+  griddep_wait();
   {
     const int chunks_per_row = Dpad / 8;
     const int d_chunks = p.D / 8;  // D % 8 == 0 is checked on the host

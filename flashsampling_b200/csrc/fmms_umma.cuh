@@ -576,6 +576,9 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         prefetch_tmap(&h_map);
       }
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
+      // The hidden states may be the output of the kernel just before this one (quantised for e4m3 weights,
+      // or gathered from host memory): their producer waits for it; the weight stream does not.
+      if (!is_w) griddep_wait();
       int it = 0;
       int st = 0;          // ring slot of the next K step, and the parity of its "empty" barrier
       uint32_t phase = 1;
@@ -723,6 +726,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
   } else if (warp >= kUmmaEpiWarp0) {
     // -------------------------------- epilogue --------------------------------
+    griddep_wait();  // temperatures and scales may come from the kernel just before this one
     const int ew = warp - kUmmaEpiWarp0;  // 0..15
     const int wg = ew >> 2;               // epilogue warpgroup 0..3
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
@@ -876,6 +880,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
   }
 
+  griddep_wait();  // every thread, before the tail reads or writes anything the previous kernel may have touched
   tc_fence_before();
   __threadfence();
   __syncthreads();

@@ -213,6 +213,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
         prefetch_tmap(&h_map);
       }
       const uint64_t pol = is_w ? policy_evict_first() : policy_evict_last();
+      if (!is_w) griddep_wait();  // the hidden states may come from the kernel just before this one
       int st = 0;          // ring slot of the next K step and the parity of its "empty" barrier (no divisions here)
       uint32_t phase = 1;
       bool ok = true;
@@ -302,6 +303,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     }
   } else if (warp >= kUmmaEpiWarp0) {
     // -------------------------------- epilogue (both CTAs) --------------------------------
+    griddep_wait();  // temperatures may come from the kernel just before this one
     const int ew = warp - kUmmaEpiWarp0;
     const int wg = ew >> 2;
     const int quad = warp & 3;
@@ -386,6 +388,7 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
     }
   }
 
+  griddep_wait();
   tc_fence_before();
   __threadfence();
   __syncthreads();
