@@ -873,8 +873,8 @@ int fmms_query_staging(int D, int B, int S, size_t* bytes) {
 // ---- top-k / top-p -----------------------------------------------------------------------
 // Scratch layout: a head that is zero between calls, laid out for 256 rows whatever the batch (calls of
 // different batch sizes share one scratch, and the parts behind the head keep stale data):
-// [table 256 x 64 u32][count 256 x 128 B][gbar, need_fallback: 256 B][row_fallback 256][ids of the
-// conditional pass 256 x 8], then [lists B x 4096 x 8][logits B x V x 4].
+// [table 256 x 64 u32][segment counts 256 x 640 u32][gbar, need_fallback: 256 B][row_fallback 256][ids of the
+// conditional pass 256 x 8], then [segments B x 640 x 16 x 8][logits B x V x 4].
 struct TopkLayout {
   size_t table, count, words, rows, dummy_idx, list, logits, total_small, total_full;
 };
@@ -883,11 +883,11 @@ static TopkLayout topk_layout(int V, int B) {
   size_t off = 0;
   const size_t rows = kMaxBatchPerLaunch;
   l.table = off;     off += align256(rows * kTopkSlots * 4);
-  l.count = off;     off += align256(rows * kTopkCountStride * 4);
+  l.count = off;     off += align256(rows * kTopkMaxSegs * 4);
   l.words = off;     off += 256;
   l.rows = off;      off += align256(rows);
   l.dummy_idx = off; off += align256(rows * 8);
-  l.list = off;      off += align256((size_t)B * kTopkListCap * 8);
+  l.list = off;      off += align256((size_t)B * kTopkMaxSegs * kTopkSegCap * 8);
   l.total_small = off;
   l.logits = off;    off += align256((size_t)B * V * 4);
   l.total_full = off;
@@ -948,7 +948,7 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
   p.topk.k = c.top_k;
   p.topk.top_p = c.top_p;
   p.topk.table = reinterpret_cast<unsigned int*>(tw + l.table);
-  p.topk.count = reinterpret_cast<unsigned int*>(tw + l.count);
+  p.topk.seg_count = reinterpret_cast<unsigned int*>(tw + l.count);
   p.topk.gbar = reinterpret_cast<unsigned int*>(tw + l.words);
   p.topk.need_fallback = p.topk.gbar + 1;
   p.topk.row_fallback = tw + l.rows;
@@ -975,7 +975,8 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
   int parts = launch_umma(*d, c.W_bf16, h_operand, p, stream, 0);
   g_overlap_next = false;
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
-  topk_finish_kernel<<<nb, kTopkFinishThreads, 0, stream>>>(p);
+  p.topk.nseg = parts / (p.B > 128 ? 2 : 1);  // CTAs x column groups (two column groups per M tile with two M tiles)
+  topk_finish_kernel<<<nb, kTopkFinishThreads, kTopkListCap * sizeof(unsigned long long), stream>>>(p);
   if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
   // 3. rows whose list overflowed: a conditional greedy pass writes all logits, then exact selection
   if (exact_pass) {

@@ -27,16 +27,17 @@ constexpr int kIdxNone = 0x7fffffff;  // candidate index meaning "no candidate y
 // that finish the rows (see fmms_topk.cuh).  Everything here is zero between calls.
 // ------------------------------------------------------------------------------------
 constexpr int kTopkSlots = 64;       // class maxima per row; also the largest top_k
-constexpr int kTopkListCap = 8192;   // candidates a row's list can hold
-constexpr int kTopkCountStride = 32; // words between two rows' counters: one 128-byte line each, so that
-                                     // the appends of different rows do not queue up behind one L2 line
+constexpr int kTopkSegCap = 16;      // candidates one epilogue thread can keep for its row (its private segment)
+constexpr int kTopkMaxSegs = 640;    // segments per row: persistent CTAs x column groups
+constexpr int kTopkListCap = 4096;   // candidates per row that the finish kernel gathers from the segments
 struct TopkArgs {
   int k;                        // top_k (1..kTopkSlots); 0 = off
   float top_p;                  // nucleus mass in (0, 1); anything else = off
+  int nseg;                     // segments per row in this launch (CTAs x column groups)
   unsigned int* table;          // [B][kTopkSlots] order-preserving keys of class maxima (0 = empty)
-  unsigned int* count;          // [B][kTopkCountStride] (first word used) candidates appended so far; above
-                                // the capacity means overflow
-  unsigned long long* list;     // [B][kTopkListCap] packed (scaled logit, local id)
+  unsigned int* seg_count;      // [B][kTopkMaxSegs] candidates each thread found (above kTopkSegCap: overflow);
+                                // every launch writes all nseg entries of every row it reads
+  unsigned long long* list;     // [B][kTopkMaxSegs][kTopkSegCap] packed (scaled logit, local id)
   unsigned int* gbar;           // grid-wide arrival counter of the collecting pass
   unsigned int* need_fallback;  // != 0: some row overflowed and the exact pass has to run
   unsigned char* row_fallback;  // [B] rows that overflowed

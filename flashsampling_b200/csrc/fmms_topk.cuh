@@ -3,17 +3,17 @@
 // The reference restricts sampling to the k largest logits of a row (and, with top-p, to the
 // smallest prefix of them whose softmax mass reaches p) by writing a top-k list per vocabulary
 // tile to memory and merging the lists afterwards (tl_fused_mm_topk.py:25-107).  Here the
-// tensor-core pass itself filters: a row's candidate list only receives logits at or above the
-// row's pivot, a running lower bound of its k-th largest logit (see the epilogue of
-// umma_sample_kernel), typically ~1e3 of the 1.5e5 entries of a row.  The kernels in this file
-// finish the rows:
+// tensor-core pass itself filters: only logits at or above the row's pivot, a running lower bound
+// of its k-th largest logit, are kept (see the epilogue of umma_sample_kernel), typically ~1e3 of
+// the 1.5e5 entries of a row, each epilogue thread in a segment of its own.  The kernels in this
+// file finish the rows:
 //
-//   topk_finish_kernel   one CTA per row: sort the row's candidates, keep the k largest, apply the
+//   topk_finish_kernel   one CTA per row: gather the row's candidates, keep the k largest, apply the
 //                        temperature-scaled softmax and the nucleus mask, and draw every sample as
 //                        a Gumbel-max over the surviving ids with the SAME noise stream as the
 //                        unrestricted sampler (noise keyed by seed, draw, row and global id), so a
 //                        restricted draw equals the unrestricted one whenever that one survives.
-//   topk_exact_kernel    rows whose list overflowed (logits arriving in ascending order defeat any
+//   topk_exact_kernel    rows that overflowed (logits rising steadily over the vocabulary defeat any
 //                        running bound): exact radix selection over the row's full logits, which a
 //                        conditional second pass has written to scratch memory.
 //   topk_overflow_kernel the same rows when the caller gave no scratch for that second pass: the
@@ -271,53 +271,66 @@ __device__ __forceinline__ void select_kth_key(const unsigned long long* keys, i
   need_eq = *sh_need;
 }
 
-// One CTA per batch row.
+// One CTA per batch row.  Dynamic shared memory: kTopkListCap keys.
 __global__ void __launch_bounds__(kTopkFinishThreads) topk_finish_kernel(const SampleParams p) {
+  extern __shared__ unsigned long long topk_keys[];
   __shared__ unsigned int hist[2048];
   __shared__ unsigned long long picked[2 * kTopkSlots];
-  __shared__ unsigned int sh_prefix, sh_need, sh_count, warp_sums[8];
+  __shared__ unsigned int sh_prefix, sh_need, sh_count, sh_total, sh_overflow, warp_sums[8];
   __shared__ TopkRowShared sh;
   const int b = blockIdx.x, tid = threadIdx.x;
-  const unsigned int cnt = p.topk.count[(size_t)b * kTopkCountStride];
-  if (cnt > (unsigned int)kTopkListCap) {
-    // the running bound did not keep up with this row: leave it to the exact pass
+  if (tid == 0) {
+    sh_total = 0u;
+    sh_overflow = 0u;
+    sh_count = 0u;
+  }
+  for (int i = tid; i < 2 * kTopkSlots; i += kTopkFinishThreads) picked[i] = 0ull;
+  __syncthreads();
+  // gather the row's candidates from the segments the epilogue threads filled (order does not matter)
+  const unsigned int* counts = p.topk.seg_count + (size_t)b * kTopkMaxSegs;
+  const unsigned long long* segs = p.topk.list + (size_t)b * kTopkMaxSegs * kTopkSegCap;
+  for (int sg = tid; sg < p.topk.nseg; sg += kTopkFinishThreads) {
+    const unsigned int c = counts[sg];
+    if (c > (unsigned int)kTopkSegCap) sh_overflow = 1u;
+    const unsigned int n = min(c, (unsigned int)kTopkSegCap);
+    if (n) {
+      const unsigned int pos = atomicAdd(&sh_total, n);
+      for (unsigned int i = 0; i < n; ++i)
+        if (pos + i < (unsigned int)kTopkListCap) topk_keys[pos + i] = segs[(size_t)sg * kTopkSegCap + i];
+    }
+  }
+  __syncthreads();
+  if (sh_overflow || sh_total > (unsigned int)kTopkListCap) {
+    // the running bound did not keep up with this row (or one thread's share of it holds more large logits
+    // than its segment): leave it to the exact pass
     if (tid == 0) {
       p.topk.row_fallback[b] = 1;
       atomicExch(p.topk.need_fallback, 1u);
     }
   } else {
     // the k largest of the row's n candidates: threshold by radix selection, then a sort of the few survivors
-    const int n = (int)cnt, k = min(p.topk.k, n);
-    const unsigned long long* topk_keys = p.topk.list + (size_t)b * kTopkListCap;  // a few KiB, read five times
-    for (int i = tid; i < 2 * kTopkSlots; i += kTopkFinishThreads) picked[i] = 0ull;
-    if (tid == 0) sh_count = 0u;
-    __syncthreads();
+    const int n = (int)sh_total, k = min(p.topk.k, n);
     uint32_t tau = 0u;
     unsigned int need_eq = 0u;
-    if (k > 0)
-      select_kth_key(topk_keys, n, k, hist, warp_sums, &sh_prefix, &sh_need, tid, kTopkFinishThreads, tau, need_eq);
+    if (k > 0) select_kth_key(topk_keys, n, k, hist, warp_sums, &sh_prefix, &sh_need, tid, kTopkFinishThreads, tau, need_eq);
     // everything above the threshold (fewer than k), then entries equal to it while there is room: which of
     // several exactly equal logits at the k-th place are taken is not specified (nor is it by the reference)
-    for (int i = tid; i < n && k > 0; i += kTopkFinishThreads) {
-      if ((uint32_t)(topk_keys[i] >> 32) > tau) picked[atomicAdd(&sh_count, 1u)] = topk_keys[i];
-    }
-    __syncthreads();
-    for (int i = tid; i < n && k > 0; i += kTopkFinishThreads) {
-      if ((uint32_t)(topk_keys[i] >> 32) == tau) {
-        const unsigned int pos = atomicAdd(&sh_count, 1u);
-        if (pos < 2u * kTopkSlots) picked[pos] = topk_keys[i];
+    for (int pass = 0; pass < 2 && k > 0; ++pass) {
+      for (int i = tid; i < n; i += kTopkFinishThreads) {
+        const uint32_t vk = (uint32_t)(topk_keys[i] >> 32);
+        if (pass == 0 ? vk > tau : vk == tau) {
+          const unsigned int pos = atomicAdd(&sh_count, 1u);
+          if (pos < 2u * kTopkSlots) picked[pos] = topk_keys[i];
+        }
       }
+      __syncthreads();
     }
-    __syncthreads();
     bitonic_sort_desc(picked, 2 * kTopkSlots, tid, kTopkFinishThreads);
     topk_finish_row(p, b, picked, k, &sh, tid, kTopkFinishThreads);
   }
   // leave the row's scratch as the next call expects it
   for (int i = tid; i < kTopkSlots; i += kTopkFinishThreads) p.topk.table[(size_t)b * kTopkSlots + i] = 0u;
-  if (tid == 0) {
-    p.topk.count[(size_t)b * kTopkCountStride] = 0u;
-    if (b == 0) *p.topk.gbar = 0u;
-  }
+  if (tid == 0 && b == 0) *p.topk.gbar = 0u;
 }
 
 // Rows that overflowed, from their full logits [B, V] (fp32, unscaled): exact radix selection of the

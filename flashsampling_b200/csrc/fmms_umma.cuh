@@ -438,10 +438,14 @@ __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const E
 }
 
 // kFlagTopk: scan columns [c_begin, c_end) of the accumulator tile: z = logit / T; track the largest z
-// seen (`tmax`) and, when `append`, add every z >= pivot to the row's candidate list.
+// seen (`tmax`) and, when `append`, keep every z >= pivot in the thread's own segment of the row's candidates
+// (`seg`, `seg_n` entries so far).  No atomics: appends through a shared per-row counter were measured first -
+// their round trips fill the SM's memory-instruction queue, which the mbarrier and TMA instructions of the
+// producer and MMA warps share, and slowed the weight stream by 25-40 us.
 template <int CW = 32>
 __device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr, int c_begin,
-                                                  int c_end, int v0, float pivot, bool append, float& tmax) {
+                                                  int c_end, int v0, float pivot, bool append,
+                                                  unsigned long long* seg, int& seg_n, float& tmax) {
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
     load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
@@ -453,9 +457,8 @@ __device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const E
           const float z = __uint_as_float(acc[i]) * e.inv_t;
           tmax = fmaxf(tmax, z);
           if (append && z >= pivot) {
-            const unsigned int pos = atomicAdd(&p.topk.count[(size_t)e.b * kTopkCountStride], 1u);
-            if (pos < (unsigned int)kTopkListCap)
-              p.topk.list[(size_t)e.b * kTopkListCap + pos] = cand_key(z, vbase + i);
+            if (seg_n < kTopkSegCap) seg[seg_n] = cand_key(z, vbase + i);
+            ++seg_n;  // beyond the capacity it only counts: the finish kernel sends the row to the exact pass
           }
         }
       }
@@ -463,19 +466,24 @@ __device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const E
   }
 }
 
-// The row's pivot: the smallest of its class maxima.  Every class maximum is a different vocabulary
-// entry, so at least kTopkSlots entries are >= the pivot and the top_k-th largest logit
-// (top_k <= kTopkSlots) cannot lie below it.  An empty class means no bound yet (-inf).
-__device__ __forceinline__ float topk_row_pivot(const SampleParams& p, int b) {
-  const uint4* t = reinterpret_cast<const uint4*>(p.topk.table + (size_t)b * kTopkSlots);
-  uint32_t lo = 0xffffffffu;
+// The rows' pivots: the smallest of each row's class maxima.  Every class maximum is a different vocabulary
+// entry, so at least kTopkSlots entries are >= the pivot and the top_k-th largest logit (top_k <= kTopkSlots)
+// cannot lie below it.  An empty class means no bound yet (-inf).  The 16 epilogue warps of the CTA share the
+// work: a warp reads a row's 64 class maxima with two coalesced loads, reduces them with shuffles and leaves the
+// pivot in shared memory.  (First version: every thread read its own row's 256 bytes, 32 different lines per
+// load instruction, four column-group warps each - 262 KB per CTA and tile from a few hot L2 lines, which slowed
+// the weight stream by 25-40 us.)
+__device__ __forceinline__ void topk_refresh_pivots(const SampleParams& p, float* pivots, int ew, int lane) {
+  for (int r = ew; r < p.B; r += kUmmaEpiWarps) {
+    const unsigned int* t = p.topk.table + (size_t)r * kTopkSlots;
+    uint32_t a, c;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(a) : "l"(t + lane));
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(c) : "l"(t + 32 + lane));
+    uint32_t lo = min(a, c);
 #pragma unroll
-  for (int i = 0; i < kTopkSlots / 4; ++i) {
-    uint4 q;
-    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(t + i));
-    lo = min(min(lo, q.x), min(q.y, min(q.z, q.w)));
+    for (int off = 16; off > 0; off >>= 1) lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+    if (lane == 0) pivots[r] = lo == 0u ? -INFINITY : float_key_decode(lo);
   }
-  return lo == 0u ? -INFINITY : float_key_decode(lo);
 }
 
 // Columns [c_begin, c_end) of the range [r_begin, r_end) that column group `g` of `groups` scans:
@@ -518,7 +526,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
   uint64_t* acc_full = empty_bar + stages;
   uint64_t* acc_empty = acc_full + 4;
   uint64_t* epi_bar = acc_empty + 4;  // two barriers of the epilogue warps (top-k: before / after the grid-wide wait)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 3);  // a third one: the per-tile pivot refresh
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -537,6 +545,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     mbar_init(&epi_bar[0], kUmmaEpiWarps);
     mbar_init(&epi_bar[1], kUmmaEpiWarps);
+    mbar_init(&epi_bar[2], kUmmaEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
     stamp(p, 0);
@@ -766,6 +775,15 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     int best_idx = kIdxNone;
     float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
     bool topk_started = false;             // kFlagTopk: the CTA's first tile has been through the grid-wide step
+    // kFlagTopk: this thread's private segment of its row's candidates
+    const int topk_seg_id = cta * kColGroups + col_group;
+    unsigned long long* topk_seg =
+        TOPK && row_ok ? p.topk.list + ((size_t)b * kTopkMaxSegs + topk_seg_id) * kTopkSegCap : nullptr;
+    int topk_seg_n = 0;
+    // the rows' pivots live in the slack behind the last pipeline stage (the MMA reads that area as operand rows
+    // that belong to no batch row; nothing else uses it)
+    float* topk_pivots = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes);
+    uint32_t pivot_phase = 0;
 
     TileWalk walk(units_total, n_tiles);
     for (int t = 0, ta = 0; t < n_tiles; ++t) {
@@ -784,18 +802,19 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       tc_fence_after();
       if (ew == 0 && lane == 0 && t == n_tiles - 1) stamp(p, 4);
       if constexpr (TOPK) {
-        // Candidates for top-k: everything at or above the row's pivot goes into the row's list.  The
-        // pivot is the smallest of kTopkSlots class maxima, to which every (CTA, warpgroup, tile)
-        // contributes the largest scaled logit it has seen.  The first tile is scanned twice: once
-        // for its maxima, then - after every CTA of the grid has published its own - for the
-        // candidates; later tiles refresh the pivot, append, and publish their maximum afterwards.
+        // Candidates for top-k: everything at or above the row's pivot goes into this thread's segment of the
+        // row's candidates.  The pivot is the smallest of kTopkSlots class maxima, to which every (CTA, column
+        // group, tile) contributes the largest scaled logit it has seen.  The first tile is scanned twice: once
+        // for its maxima, then - after every CTA of the grid has published its own - for the candidates;
+        // later tiles refresh the pivots, collect, and publish their maximum afterwards.
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         // odd multipliers: every row reaches all slots, and every slot hears from all column groups (whose
         // shares of a tile differ in width), so that no class is made of narrow shares only
         const int slot = (cta * 5 + (m_tile * kColGroups + col_group) * 17 + 37 * t) & (kTopkSlots - 1);
         float tmax = -INFINITY;
-        if (!topk_started) {
-          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, 0.f, false, tmax);
+        const bool first_tile = !topk_started;
+        if (first_tile) {
+          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, 0.f, false, topk_seg, topk_seg_n, tmax);
           if (row_ok && tmax > -INFINITY) atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
           __threadfence();
           __syncwarp();
@@ -820,13 +839,18 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
           ok = ok && mbar_wait(&epi_bar[1], 0u, abort_flag, p.status_dev);
           if (!ok) break;
           topk_started = true;
-          const float pivot = row_ok ? topk_row_pivot(p, b) : INFINITY;
-          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, tmax);
-        } else {
-          const float pivot = row_ok ? topk_row_pivot(p, b) : INFINITY;
-          if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, tmax);
-          if (row_ok && tmax > -INFINITY) atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
         }
+        // this tile's pivots, computed by all epilogue warps together
+        topk_refresh_pivots(p, topk_pivots, ew, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&epi_bar[2]);
+        if (!mbar_wait(&epi_bar[2], pivot_phase, abort_flag, p.status_dev)) break;
+        pivot_phase ^= 1u;
+        const float pivot = row_ok ? topk_pivots[b] : INFINITY;
+        if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, topk_seg, topk_seg_n, tmax);
+        // later tiles publish their maximum after the scan (the first tile's went out before the grid-wide wait)
+        if (!first_tile && row_ok && tmax > -INFINITY)
+          atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
       } else if (warp_ok) {
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         if constexpr (LSE) {
@@ -861,6 +885,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       if (lane == 0) mbar_arrive(&acc_empty[j]);
     }
     if (ew == 0 && lane == 0) stamp(p, 5);
+    if (TOPK && row_ok) p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id] = (unsigned int)topk_seg_n;
     // merge this thread's winners into the per-(row, draw) keys
     if (!TOPK && row_ok) {
       if (S == 1) {

@@ -262,12 +262,14 @@ int fmms_run(const fmms_call_t* call);
  * logits of a row, optionally cut to the smallest prefix (in descending order) whose mass before
  * each kept entry is below top_p (the most probable entry always stays), renormalised.
  *
- * Here the tensor-core pass appends to a per-row list only the logits at or above a running
- * lower bound of the row's k-th largest logit (about 1e3 of 1.5e5 entries); one small kernel per
- * call then sorts each row's list, applies softmax and the nucleus cut and draws the samples as a
+ * Here the tensor-core pass keeps, per row, only the logits at or above a running lower bound of
+ * the row's k-th largest logit (about 1e3 of 1.5e5 entries; every epilogue thread has a segment of
+ * 16 entries per row); one small kernel per call then gathers each row's candidates, selects the
+ * k largest, applies softmax and the nucleus cut and draws the samples as a
  * Gumbel-max over the surviving ids, with the noise stream of fmms_sample() (so a draw equals the
- * unrestricted draw for the same seed whenever that one survives the cut).  A row whose list
- * overflows (4096 entries; logits that arrive in ascending order do that) is redone exactly by a
+ * unrestricted draw for the same seed whenever that one survives the cut).  A row that overflows
+ * (more than 4096 candidates, or more than 16 in one thread's share of ~300 vocabulary entries;
+ * logits that rise steadily over the vocabulary do that) is redone exactly by a
  * second pass that materialises its logits - launched with every call, it returns at once when
  * no row needs it.  out_logprob / out_lse, when given, refer to the truncated distribution.
  *
