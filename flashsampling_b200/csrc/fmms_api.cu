@@ -434,7 +434,9 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   }
   if (rc != kOk) return -rc;
   if (umma_m64() >= 0 && pl.mt == 1 && pl.copies == 1 && pl.h_rows <= 64) pl.m_rows = umma_m64() ? 64 : 128;
-  if (pl.copies > 1) {
+  if (pl.m_rows == 64 && p.S > 1 && !(p.flags & kFlagTopk) && (size_t)128 * p.S > cand_capacity)
+    pl.m_rows = 128;  // the split epilogue of 64-row accumulators keeps the S > 1 scratch by TMEM lane as well
+  if (pl.copies > 1 || (pl.m_rows == 64 && p.S > 1 && !(p.flags & kFlagTopk))) {
     p.cand_rows = 128;
     p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * 128 * p.S);
   }

@@ -137,12 +137,11 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   const int low_units = pl.q_units > 1 ? pl.q_units - 1 : pl.q_units;
   while (r > 1 && (size_t)pl.slabs * low_units * 16 * 128 < (size_t)(r - 1) * (16384 / r)) r >>= 1;
   pl.copies = r;
-  // M = 64 MMAs read half the A operand and leave 16 rows in the lower half of every TMEM lane quadrant.  Measured
-  // against M = 128 in the same run (Qwen head): B = 4 210 -> 200 us, B = 16 203.7 -> 199.7, B = 64 217 -> 213
-  // (last-tile epilogue 9.5 -> 6.9 us), Llama head B = 64 367 -> 351; but B = 32 203.6 -> 213.7: every step with
-  // two or more active lane quadrants is ~10 us slower than one with a single quadrant, whatever M is, and M = 64
-  // spreads 17..32 rows over two quadrants where M = 128 keeps them in one.
-  pl.m_rows = (pl.mt == 1 && r == 1 && (pl.h_rows <= 16 || (pl.h_rows > 32 && pl.h_rows <= 64))) ? 64 : 128;
+  // M = 64 MMAs read half the A operand and leave 16 rows in the lower half of every TMEM lane quadrant; the
+  // epilogue splits every chunk of columns between the two half-warps, so twice as many lanes scan as with the
+  // same rows in an M = 128 accumulator.  Measured against M = 128 in the same run (Qwen head): B = 16
+  // 197.6 -> 194.1 us, B = 32 199.7 -> 196.6, B = 64 217 -> 197.6, four draws per row at B = 64 253 -> 232.
+  pl.m_rows = (pl.mt == 1 && r == 1 && pl.h_rows <= 64) ? 64 : 128;
   return pl;
 }
 
@@ -321,119 +320,162 @@ __device__ __forceinline__ void load_logit_chunk(const SampleParams& p, const Ep
   }
 }
 
-// kFlagLogprob: fold the scaled logits of columns [c_begin, c_end) of the accumulator tile into
-// the thread's running log-sum-exp - one maximum and one rescale per CW-column chunk.  A pass of
-// its own over the tile (TMEM reads are cheap), so that the sampling scan keeps its registers.
+// kFlagLogprob: fold the first n_ok of NC scaled logits into the thread's running log-sum-exp - one maximum and
+// one rescale per chunk.
+template <int NC>
+__device__ __forceinline__ void lse_chunk(const uint32_t (&acc)[NC], int n_ok, float sc, float& lse_m, float& lse_l) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NC; ++i)
+    if (i < n_ok) mx = fmaxf(mx, __uint_as_float(acc[i]));
+  if (mx > -INFINITY) {
+    const float mn = fmaxf(lse_m, mx * sc);
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NC; i += 2) {
+      if (i < n_ok) sum0 += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
+      if (i + 1 < n_ok) sum1 += ex2_approx(fmaf(__uint_as_float(acc[i + 1]), sc, -mn));
+    }
+    lse_l = lse_l * ex2_approx(lse_m - mn) + (sum0 + sum1);
+    lse_m = mn;
+  }
+}
+
+// The upper 16 columns of a 32-column chunk move from the lanes that hold the rows (0..15) to lanes 16..31, so that
+// both half-warps work on an M = 64 accumulator; afterwards every lane holds 16 columns of the row of (lane & 15),
+// the first of them column 0 of the chunk in lanes 0..15 and column 16 in lanes 16..31.
+__device__ __forceinline__ void split_chunk(const uint32_t (&acc)[32], uint32_t (&half)[16]) {
+  const int lane = (int)(threadIdx.x & 31);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t up = __shfl_sync(0xffffffffu, acc[16 + i], lane & 15);
+    half[i] = (lane & 16) ? up : acc[i];
+  }
+}
+
+// kFlagLogprob: fold the scaled logits of columns [c_begin, c_end) of the accumulator tile into the thread's running
+// log-sum-exp.  A pass of its own over the tile (TMEM reads are cheap), so that the sampling scan keeps its
+// registers.  `split`: see scan_tile_columns; the two lanes of a row keep separate sums.
 template <int CW = 32>
 __device__ __forceinline__ void lse_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
-                                                 int c_begin, int c_end, int v0, float& lse_m, float& lse_l) {
+                                                 int c_begin, int c_end, int v0, float& lse_m, float& lse_l,
+                                                 bool split = false) {
   const float sc = e.inv_t * kLog2e;  // > 0: the largest logit gives the largest scaled logit
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
     load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
-    if (e.row_ok) {
-      const int n_ok = min(c_end - c, p.V - (v0 + c));  // valid columns of this chunk
-      float mx = -INFINITY;
+    if constexpr (CW == 32) {
+      if (split) {
+        uint32_t half[16];
+        split_chunk(acc, half);
+        const int cc = c + (int)(threadIdx.x & 16);
+        if (e.row_ok) lse_chunk<16>(half, min(c_end - cc, p.V - (v0 + cc)), sc, lse_m, lse_l);
+        continue;
+      }
+    }
+    if (e.row_ok) lse_chunk<CW>(acc, min(c_end - c, p.V - (v0 + c)), sc, lse_m, lse_l);
+  }
+}
+
+// NC consecutive columns of the thread's row, starting at column c of the tile (vocabulary row v0 + c of this shard),
+// for draw `s`: scale, add noise, keep the running (max, id).
+template <int NC>
+__device__ __forceinline__ void scan_chunk(const SampleParams& p, const EpiRow& e, const uint32_t (&acc)[NC], int c, int c_end,
+                                           int v0, int s, float& bv, int& bi) {
+  const int vbase = v0 + c;
+  if (e.ret_logits && s == 0) {
 #pragma unroll
-      for (int i = 0; i < CW; ++i)
-        if (i < n_ok) mx = fmaxf(mx, __uint_as_float(acc[i]));
-      if (mx > -INFINITY) {
-        const float mn = fmaxf(lse_m, mx * sc);
-        float sum0 = 0.f, sum1 = 0.f;
+    for (int i = 0; i < NC; ++i)
+      if (c + i < c_end && vbase + i < p.V)
+        p.logits_out[(size_t)e.b * p.V + vbase + i] = __uint_as_float(acc[i]);
+  }
+  if (e.greedy) {
 #pragma unroll
-        for (int i = 0; i < CW; i += 2) {
-          if (i < n_ok) sum0 += ex2_approx(fmaf(__uint_as_float(acc[i]), sc, -mn));
-          if (i + 1 < n_ok) sum1 += ex2_approx(fmaf(__uint_as_float(acc[i + 1]), sc, -mn));
+    for (int i = 0; i < NC; ++i) {
+      const float y = __uint_as_float(acc[i]);
+      if (c + i < c_end && vbase + i < p.V && y > bv) {
+        bv = y;
+        bi = vbase + i;
+      }
+    }
+  } else if (e.ext) {
+    const float* nz = p.ext_noise + (size_t)s * p.noise_s_stride + (size_t)e.b * p.noise_ld + vbase;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      if (c + i < c_end && vbase + i < p.V) {
+        const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? nz[i] : 0.f);
+        if (y > bv) {
+          bv = y;
+          bi = vbase + i;
         }
-        lse_l = lse_l * ex2_approx(lse_m - mn) + (sum0 + sum1);
-        lse_m = mn;
+      }
+    }
+  } else if (!e.noisy) {
+    // a row with temperature <= 0 inside a sampled batch: plain argmax, no noise to draw
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const float y = __uint_as_float(acc[i]) * e.inv_t;
+      if (c + i < c_end && vbase + i < p.V && y > bv) {
+        bv = y;
+        bi = vbase + i;
+      }
+    }
+  } else if (e.quad_aligned) {
+    const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
+#pragma unroll
+    for (int g = 0; g < NC / 4; ++g) {
+      const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      // (A cheap screen in front of the exact comparison - the leading random bits against
+      // 2^((x / T - best) log2 e), one ex2 instead of a conversion and two logarithms, exact path for the
+      // survivors - was measured and dropped: the last tile of a 5-tile range got 16 % faster, but a
+      // CTA's first tile, where new records are frequent and the warp runs both paths, got 14 %
+      // slower, and short tensor-parallel shards consist of that tile alone.)
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        const int i = g * 4 + wi;
+        const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
+        if (c + i < c_end && vbase + i < p.V && y > bv) {
+          bv = y;
+          bi = vbase + i;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
+      const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, vg >> 2);
+      const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)) : 0.f);
+      if (c + i < c_end && vbase + i < p.V && y > bv) {
+        bv = y;
+        bi = vbase + i;
       }
     }
   }
 }
 
 // Scan columns [c_begin, c_end) of the accumulator tile at TMEM address `t_addr` (this warp's lane
-// quadrant, first column of the tile) for draw `s`: scale, add noise, keep the running (max, id)
-// of the thread's row.  The tile's first column is vocabulary row v0 of this shard.
+// quadrant, first column of the tile) for draw `s`.  `split` (M = 64 accumulators: only lanes 0..15 of a quadrant
+// hold rows): lanes 16..31 fetch the upper 16 columns of each 32-column chunk from the lane that holds the row
+// (16 shuffles) and scan them for that row, so that both halves of the warp work; the two lanes of a row keep
+// separate running winners, which meet in the row's packed key at the end of the kernel.
 template <int CW = 32>
 __device__ __forceinline__ void scan_tile_columns(const SampleParams& p, const EpiRow& e, uint32_t t_addr,
-                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi) {
+                                                  int c_begin, int c_end, int v0, int s, float& bv, int& bi,
+                                                  bool split = false) {
   for (int c = c_begin; c < c_end; c += CW) {
     uint32_t acc[CW];
     load_logit_chunk<CW>(p, e, t_addr + (uint32_t)c, v0 + c, acc);
-    if (e.row_ok) {
-      const int vbase = v0 + c;
-      if (e.ret_logits && s == 0) {
-#pragma unroll
-        for (int i = 0; i < CW; ++i)
-          if (c + i < c_end && vbase + i < p.V)
-            p.logits_out[(size_t)e.b * p.V + vbase + i] = __uint_as_float(acc[i]);
-      }
-      if (e.greedy) {
-#pragma unroll
-        for (int i = 0; i < CW; ++i) {
-          const float y = __uint_as_float(acc[i]);
-          if (c + i < c_end && vbase + i < p.V && y > bv) {
-            bv = y;
-            bi = vbase + i;
-          }
-        }
-      } else if (e.ext) {
-        const float* nz = p.ext_noise + (size_t)s * p.noise_s_stride + (size_t)e.b * p.noise_ld + vbase;
-#pragma unroll
-        for (int i = 0; i < CW; ++i) {
-          if (c + i < c_end && vbase + i < p.V) {
-            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? nz[i] : 0.f);
-            if (y > bv) {
-              bv = y;
-              bi = vbase + i;
-            }
-          }
-        }
-      } else if (!e.noisy) {
-        // a row with temperature <= 0 inside a sampled batch: plain argmax, no noise to draw
-#pragma unroll
-        for (int i = 0; i < CW; ++i) {
-          const float y = __uint_as_float(acc[i]) * e.inv_t;
-          if (c + i < c_end && vbase + i < p.V && y > bv) {
-            bv = y;
-            bi = vbase + i;
-          }
-        }
-      } else if (e.quad_aligned) {
-        const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
-#pragma unroll
-        for (int g = 0; g < CW / 4; ++g) {
-          const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-          // (A cheap screen in front of the exact comparison - the leading random bits against
-          // 2^((x / T - best) log2 e), one ex2 instead of a conversion and two logarithms, exact path for the
-          // survivors - was measured and dropped: the last tile of a 5-tile range got 16 % faster, but a
-          // CTA's first tile, where new records are frequent and the warp runs both paths, got 14 %
-          // slower, and short tensor-parallel shards consist of that tile alone.)
-#pragma unroll
-          for (int wi = 0; wi < 4; ++wi) {
-            const int i = g * 4 + wi;
-            const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
-            if (c + i < c_end && vbase + i < p.V && y > bv) {
-              bv = y;
-              bi = vbase + i;
-            }
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < CW; ++i) {
-          const unsigned long long vg = (unsigned long long)(p.v_offset + vbase + i);
-          const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, vg >> 2);
-          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, e.noisy ? gumbel_from_bits(pick_word(q, (uint32_t)vg & 3u)) : 0.f);
-          if (c + i < c_end && vbase + i < p.V && y > bv) {
-            bv = y;
-            bi = vbase + i;
-          }
-        }
+    if constexpr (CW == 32) {
+      if (split) {
+        uint32_t half[16];
+        split_chunk(acc, half);
+        if (e.row_ok) scan_chunk<16>(p, e, half, c + (int)(threadIdx.x & 16), c_end, v0, s, bv, bi);
+        continue;
       }
     }
+    if (e.row_ok) scan_chunk<CW>(p, e, acc, c, c_end, v0, s, bv, bi);
   }
 }
 
@@ -746,10 +788,17 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     // the replica whose rows sit in this quadrant's lanes, and the batch row of this thread
     const int lanes_per_replica = 128 / R;
     const int replica = (quad * 32) / lanes_per_replica;
-    const int b = m64 ? quad * 16 + lane : m_tile * 128 + quad * 32 + lane - replica * lanes_per_replica;
-    const bool row_ok = m64 ? (lane < 16 && b < p.B) : b < p.B;
+    // M = 64 accumulators keep rows in lanes 0..15 of each quadrant only.  The sampling scan then splits every
+    // chunk of columns between the two half-warps (lanes 16..31 work for the row of lane - 16), and so does the
+    // log-sum-exp scan; the top-k scan leaves the upper lanes idle.
+    const bool split = m64 && !TOPK;
+    const int b = m64 ? quad * 16 + (lane & 15) : m_tile * 128 + quad * 32 + lane - replica * lanes_per_replica;
+    const bool holds_acc = !m64 || lane < 16;               // this lane's TMEM lane carries a batch row
+    const bool row_ok = b < p.B && (split || holds_acc);    // this thread scans for row b
+    const bool acc_ok = b < p.B && holds_acc;
     const bool warp_ok = m64 ? quad * 16 < p.B : (m_tile * 128 + quad * 32 - replica * lanes_per_replica) < p.B;
-    const int cand_row = (R > 1) ? quad * 32 + lane : b;  // row of the S > 1 scratch: replicas must not share one
+    // row of the S > 1 scratch: replicas, and the two lanes of a split row, must not share one
+    const int cand_row = (R > 1 || split) ? quad * 32 + lane : b;
 
     const bool greedy = (p.flags & kFlagGreedy) != 0;
     const bool ext = (p.flags & kFlagExtNoise) != 0;
@@ -855,7 +904,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((j * MT + m_tile) * nt_cap);
         if constexpr (LSE) {
           if (narrow) lse_tile_columns<16>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
-          else lse_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l);
+          else lse_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, lse_m, lse_l, split);
         }
         for (int s = 0; s < S; ++s) {
           float bv = best_val;
@@ -865,7 +914,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
             bi = kIdxNone;
           }
           if (narrow) scan_tile_columns<16>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
-          else scan_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi);
+          else scan_tile_columns<32>(p, row, t_addr, c_begin, c_end, v0, s, bv, bi, split);
           if (S > 1) {
             if (row_ok) {
               const size_t o = slot_row + (size_t)s * p.cand_rows + cand_row;
@@ -885,6 +934,11 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       if (lane == 0) mbar_arrive(&acc_empty[j]);
     }
     if (ew == 0 && lane == 0) stamp(p, 5);
+    if (LSE && split) {
+      // the upper half-warp's sums join those of the lanes that hold the rows
+      const float m2 = __shfl_down_sync(0xffffffffu, lse_m, 16), l2 = __shfl_down_sync(0xffffffffu, lse_l, 16);
+      if (lane < 16) lse_merge(lse_m, lse_l, m2, l2);
+    }
     if (TOPK && row_ok) p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id] = (unsigned int)topk_seg_n;
     // merge this thread's winners into the per-(row, draw) keys
     if (!TOPK && row_ok) {
@@ -899,7 +953,7 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       }
       // every tile has been multiplied, so the pipeline's first stage is free: it collects the
       // partial sums of each row, one per (replica, column group)
-      if constexpr (LSE)
+      if (LSE && acc_ok)
         reinterpret_cast<unsigned long long*>(smem)[(replica * kColGroups + col_group) * (MT * 128) + b] =
             lse_pack(lse_m, lse_l);
     }

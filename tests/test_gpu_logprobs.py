@@ -144,7 +144,9 @@ def test_c_abi_reports_the_log_normaliser_and_rejects_unsupported_modes(fs):
     want_lp, want_lse = O.log_probs(O.logits_fp32(w, h), 0.8, out.cpu())
     assert (lp.cpu().double() - want_lp).abs().max() < ATOL
     assert (lse.cpu().double() - want_lse).abs().max() < ATOL
-    keys_at = wsz - B * S * 8 * 641  # the head (CTA counter, log-sum-exp scratch) precedes the packed winners
+    # the head (CTA counter, log-sum-exp scratch) precedes the packed winners; with several draws per row the
+    # workspace is sized for 128 rows (one per TMEM lane), each item 8 bytes of key + 640 x 8 of candidates
+    keys_at = wsz - 128 * S * 8 * 641
     assert int(ws[:256].count_nonzero()) == 0 and int(ws[keys_at:keys_at + B * S * 8].count_nonzero()) == 0
     # the log-probability output is required; the two-stage mode does not carry it
     assert lib.fmms_sample_logprobs(*args, 0, *tail, None, None) == _lib.ERR_BAD_ARG
