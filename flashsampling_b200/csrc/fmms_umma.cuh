@@ -941,9 +941,28 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     }
     if (TOPK && row_ok) p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id] = (unsigned int)topk_seg_n;
     // merge this thread's winners into the per-(row, draw) keys
+    if (!TOPK && S == 1 && R == 1) {
+      // One key per row and CTA: the winners of a row's column groups (and half-warps) meet in shared memory,
+      // in the slack behind the last pipeline stage, before one thread per row merges them into the global key.
+      unsigned long long* cta_keys = reinterpret_cast<unsigned long long*>(smem + (size_t)stages * stage_bytes);
+      const int halves = split ? 2 : 1;
+      if (row_ok)
+        cta_keys[(size_t)(col_group * halves + (split ? (lane >> 4) : 0)) * (MT * 128) + b] =
+            best_idx != kIdxNone ? cand_key(best_val, best_idx) : 0ull;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&epi_bar[0]);
+      if (mbar_wait(&epi_bar[0], 0u, abort_flag, p.status_dev)) {
+        const int r = ew * 32 + lane;
+        if (r < MT * 128 && r < p.B) {
+          unsigned long long k = 0ull;
+          for (int g = 0; g < kColGroups * halves; ++g) k = max(k, cta_keys[(size_t)g * (MT * 128) + r]);
+          if (k != 0ull) atomicMax(&p.keys[r], k);
+        }
+      }
+    }
     if (!TOPK && row_ok) {
       if (S == 1) {
-        if (best_idx != kIdxNone) atomicMax(&p.keys[b], cand_key(best_val, best_idx));
+        if (R > 1 && best_idx != kIdxNone) atomicMax(&p.keys[b], cand_key(best_val, best_idx));
       } else {
         for (int s = 0; s < S; ++s) {
           const size_t o = slot_row + (size_t)s * p.cand_rows + cand_row;

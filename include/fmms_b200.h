@@ -178,8 +178,10 @@ int fmms_sample_tp(const void* W_bf16, const void* H_bf16, const float* temperat
  * reproducible with the tensor-core kernels; to fp32 rounding with the weight-streaming kernel,
  * whose CTAs share part of the work dynamically); the winner's logit is its perturbed value minus its own noise, which is a
  * pure function of (seed, draw, row, id).  The sampled ids are those of fmms_sample().  Not combined
- * with FMMS_FLAG_TWO_STAGE or with fmms_sample_tp() (FMMS_ERR_UNSUPPORTED): under tensor
- * parallelism call this on the local shard and combine out_lse across ranks.
+ * with FMMS_FLAG_TWO_STAGE (FMMS_ERR_UNSUPPORTED).  This entry point has no tensor-parallel
+ * arguments: under tensor parallelism use fmms_run() with FMMS_FLAG_LOGPROB and tp_world > 1 (the
+ * winner's logit and every rank's log-sum-exp travel in the same fused exchange as the winners), or
+ * call this on the local shard and combine out_lse across ranks on the host.
  * The reference has no counterpart: it lists log-probabilities as unavailable without the full
  * logits (findings/vllm-integration.md:99); the accumulation is the online log-sum-exp that its
  * paper's appendix on optional outputs describes. */
