@@ -422,6 +422,8 @@ __device__ __forceinline__ void scan_chunk(const SampleParams& p, const EpiRow& 
     }
   } else if (e.quad_aligned) {
     const unsigned long long q0 = (unsigned long long)(p.v_offset + vbase) >> 2;
+    const int n_ok = min(c_end - c, p.V - vbase);  // valid columns of this chunk
+    int li = -1;  // column (inside the chunk) of a new running maximum: the selects then take immediates
 #pragma unroll
     for (int g = 0; g < NC / 4; ++g) {
       const uint4 q = noise_block(e.seed, s, e.b + p.b_offset, q0 + g);
@@ -431,16 +433,29 @@ __device__ __forceinline__ void scan_chunk(const SampleParams& p, const EpiRow& 
       // survivors - was measured and dropped: the last tile of a 5-tile range got 16 % faster, but a
       // CTA's first tile, where new records are frequent and the warp runs both paths, got 14 %
       // slower, and short tensor-parallel shards consist of that tile alone.)
+      if (n_ok >= NC) {  // an interior chunk: no column masks
 #pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
-        const int i = g * 4 + wi;
-        const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
-        if (c + i < c_end && vbase + i < p.V && y > bv) {
-          bv = y;
-          bi = vbase + i;
+        for (int wi = 0; wi < 4; ++wi) {
+          const int i = g * 4 + wi;
+          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
+          if (y > bv) {
+            bv = y;
+            li = i;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const int i = g * 4 + wi;
+          const float y = fmaf(__uint_as_float(acc[i]), e.inv_t, gumbel_from_bits(w[wi]));
+          if (i < n_ok && y > bv) {
+            bv = y;
+            li = i;
+          }
         }
       }
     }
+    if (li >= 0) bi = vbase + li;
   } else {
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
