@@ -421,21 +421,21 @@ static int launch_umma(DeviceInfo& d, const void* W, const void* H, SampleParams
   // Row replicas keep the S > 1 scratch by TMEM lane (128 rows): without room for that, run without them.
   const int copies_cap =
       ((p.flags & kFlagTopk) || (p.S > 1 && (size_t)128 * p.S > cand_capacity)) ? 1 : umma_copies_cap();
+  // The split epilogue of 64-row accumulators keeps the S > 1 scratch by TMEM lane as well.
+  int m_force = umma_m64();
+  if (p.S > 1 && !(p.flags & kFlagTopk) && (size_t)128 * p.S > cand_capacity) m_force = 0;
   UmmaPlan pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(),
-                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), copies_cap);
+                          umma_nt_target(), umma_min_tiles(), p.D, umma_slabs_force(), copies_cap, m_force);
   if (pl.grid * kUmmaEpiGroups > kMaxParts) return -kErrUnsupported;
   UmmaMaps mp;
   int rc = build_umma_maps(W, H, p, pl, &mp);
   if (rc != kOk && pl.slabs > 1) {
     // the driver refused the 3-D view: fall back to one slab per operation
     pl = umma_plan(p.V, p.B, d.num_sms, d.max_smem_optin, umma_stage_cap(), umma_mt2_nt_cap(), umma_nt_target(),
-                   umma_min_tiles(), 0, 0, copies_cap);
+                   umma_min_tiles(), 0, 0, copies_cap, m_force);
     rc = build_umma_maps(W, H, p, pl, &mp);
   }
   if (rc != kOk) return -rc;
-  if (umma_m64() >= 0 && pl.mt == 1 && pl.copies == 1 && pl.h_rows <= 64) pl.m_rows = umma_m64() ? 64 : 128;
-  if (pl.m_rows == 64 && p.S > 1 && !(p.flags & kFlagTopk) && (size_t)128 * p.S > cand_capacity)
-    pl.m_rows = 128;  // the split epilogue of 64-row accumulators keeps the S > 1 scratch by TMEM lane as well
   if (pl.copies > 1 || (pl.m_rows == 64 && p.S > 1 && !(p.flags & kFlagTopk))) {
     p.cand_rows = 128;
     p.cand_idx = reinterpret_cast<int*>(p.cand_val + (size_t)kMaxParts * 128 * p.S);

@@ -62,8 +62,8 @@ struct UmmaPlan {
 };
 
 // Shared memory: [barriers 1 KiB][stages x (W tile: tallest tile x 128 B | MT hidden-state tiles:
-// h_rows x 128 B)][16 KiB slack].  With fewer than 128 hidden-state rows the MMA's 128-row A
-// operand runs past its tile into whatever follows (the next stage, or the slack after the last
+// h_rows x 128 B)][8 or 16 KiB slack].  With fewer hidden-state rows than the MMA's M (64 or 128) the
+// A operand runs past its tile into whatever follows (the next stage, or the slack after the last
 // one); those accumulator lanes belong to no batch row and are never read.
 __host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_rows, int slabs) {
   return (size_t)slabs * ((size_t)q_units * 16 * 128 + (size_t)mt * h_rows * 128);
@@ -75,7 +75,7 @@ __host__ __device__ inline size_t umma_stage_bytes(int mt, int q_units, int h_ro
 // CTAs are then q or q - 1 units high, which two TMA descriptors (two box heights) cover.
 __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int stages_cap = 0,
                                    int mt2_nt_cap = 256, int nt_target = 0, int min_tiles = 1, int D = 0, int slabs_force = 0,
-                                   int copies_cap = 0) {
+                                   int copies_cap = 0, int m_force = -1) {
   UmmaPlan pl{};
   pl.mt = B > 128 ? 2 : 1;
   // Two M tiles share each W tile.  Wide tiles (one 2 x 256-column accumulator, epilogue not
@@ -86,11 +86,21 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
   int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
+  // M = 64 MMAs (at most 64 batch rows, no row replicas; m_force = 0 keeps M = 128) read half the A operand and
+  // leave 16 rows in the lower half of every TMEM lane quadrant; the epilogue splits every chunk of columns
+  // between the two half-warps, so twice as many lanes scan as with the same rows in an M = 128 accumulator.
+  // Measured against M = 128 in the same run (Qwen head): B = 16 197.6 -> 194.1 us, B = 32 199.7 -> 196.6,
+  // B = 64 217 -> 197.6, four draws per row at B = 64 253 -> 232.
+  pl.m_rows = (pl.mt == 1 && copies_cap < 2 && pl.h_rows <= 64 && m_force != 0) ? 64 : 128;
+  // Behind the last stage: room for the rows the MMA's A operand reads beyond its hidden-state tile
+  // ((m_rows - h_rows) x 128 B; with row replicas up to 16 KiB), which the epilogue reuses for the rows' pivots
+  // (top-k) and the CTA's winners (at most 8 KiB).
+  const size_t slack = (copies_cap >= 2 || (pl.mt == 1 && pl.m_rows - pl.h_rows > 56)) ? kUmmaHTileMax : kUmmaHTileMax / 2;
   int cap_units = pl.nt_cap / 16;
   if (pl.mt == 1 && pl.h_rows <= 64 && D > 0 && D % 64 == 0) {
     // keep tiles low enough for two K slabs per stage and three stages (the 52 KiB operations
     // are worth more than the last 48 rows of tile height)
-    const long long per_stage = ((long long)max_smem - (1024 + 1024 + kUmmaHTileMax)) / 3;
+    const long long per_stage = ((long long)max_smem - (1024 + 1024 + (long long)slack)) / 3;
     const int fit = (int)((per_stage / 2 - (long long)pl.h_rows * 128) / (16 * 128));
     if (fit >= 8 && fit < cap_units) cap_units = fit;
   }
@@ -105,7 +115,7 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   // several 64-column slabs of the hidden dimension per operation (a 3-D box), aiming at >= 40 KiB
   // of W per operation (measured: 52 KiB operations stream the Qwen head 4% faster than 26 KiB ones).  Needs D % 64 == 0 (a slab index must not run into the next row).
   pl.slabs = 1;
-  const size_t fixed = 1024 /*barriers*/ + 1024 /*alignment*/ + kUmmaHTileMax /*A-operand overrun*/;
+  const size_t fixed = 1024 /*barriers*/ + 1024 /*alignment*/ + slack;
   if (D > 0 && D % 64 == 0) {
     const int w_slab = pl.q_units * 16 * 128;
     int sk = slabs_force > 0 ? slabs_force : (40 * 1024 + w_slab - 1) / w_slab;
@@ -137,11 +147,7 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   const int low_units = pl.q_units > 1 ? pl.q_units - 1 : pl.q_units;
   while (r > 1 && (size_t)pl.slabs * low_units * 16 * 128 < (size_t)(r - 1) * (16384 / r)) r >>= 1;
   pl.copies = r;
-  // M = 64 MMAs read half the A operand and leave 16 rows in the lower half of every TMEM lane quadrant; the
-  // epilogue splits every chunk of columns between the two half-warps, so twice as many lanes scan as with the
-  // same rows in an M = 128 accumulator.  Measured against M = 128 in the same run (Qwen head): B = 16
-  // 197.6 -> 194.1 us, B = 32 199.7 -> 196.6, B = 64 217 -> 197.6, four draws per row at B = 64 253 -> 232.
-  pl.m_rows = (pl.mt == 1 && r == 1 && pl.h_rows <= 64) ? 64 : 128;
+  if (r > 1) pl.m_rows = 128;
   return pl;
 }
 
