@@ -777,7 +777,8 @@ static int sample_rows(const void* W_bf16, const void* H_bf16, const float* temp
     p.h_scale = hs;
     p.D = D / 2;
     g_overlap_next = true;  // the weight stream starts while the quantiser runs
-    const int parts8 = launch_umma(*d, W_bf16, hq, p, stream, cap);
+    const int parts8 = use_pair_kernel(V_local, p.D, B, d->num_sms) ? launch_umma_pair(*d, W_bf16, hq, p, stream)
+                                                                     : launch_umma(*d, W_bf16, hq, p, stream, cap);
     g_overlap_next = false;
     g_last_path = FMMS_PATH_MMA;
     if (parts8 <= 0) return parts8 == 0 ? FMMS_ERR_CUDA : -parts8;

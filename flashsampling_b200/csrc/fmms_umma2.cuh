@@ -115,9 +115,22 @@ __device__ __forceinline__ void umma_pair_bf16(uint32_t tmem_d, uint64_t adesc, 
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// fp32 accumulate, bf16 x bf16, both K-major, M = 256 (128 rows in each CTA of the pair)
-__host__ __device__ inline uint32_t umma_pair_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+__device__ __forceinline__ void umma_pair_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// fp32 accumulate, bf16 x bf16 (or e4m3 x e4m3: format code 0 of kind::f8f6f4), both K-major, M = 256 (128 rows in
+// each CTA of the pair)
+__host__ __device__ inline uint32_t umma_pair_idesc(int n, bool fp8 = false) {
+  const uint32_t fmt = fp8 ? 0u : ((1u << 7) | (1u << 10));
+  return (1u << 4) | fmt | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 // Tile schedule of one pair: granules of 32 rows, T near-equal tiles (see TileWalk).
@@ -253,12 +266,13 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
       bool first = true;
       bool ok = true;
       const uint32_t smem0 = smem_u32(smem);
+      const bool fp8 = (p.flags & kFlagFp8) != 0;
       PairWalk walk(units_total, n_tiles);
       for (int t = 0; t < n_tiles && ok; ++t) {
         int v0, NT;
         walk.next(v0, NT);
         if (NT == 0) continue;
-        const uint32_t idesc = umma_pair_idesc(NT);
+        const uint32_t idesc = umma_pair_idesc(NT, fp8);
         const uint32_t w_pitch = (uint32_t)((NT / 2) * 128);
         if (!mbar_wait(&acc_empty[j], acc_phase ^ 1u, abort_flag, p.status_dev)) break;
         tc_fence_after();
@@ -277,10 +291,18 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
           for (int sl = 0; sl < SK; ++sl) {
             const uint64_t bdesc = umma_smem_desc(sw + (uint32_t)sl * w_pitch);
             const uint64_t adesc = umma_smem_desc(sw + (uint32_t)(w_tile_bytes + sl * h_slab_bytes));
-            umma_pair_bf16(d_tmem, adesc, bdesc, idesc, (kb | sl) != 0 ? 1u : 0u);
-            umma_pair_bf16(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
-            umma_pair_bf16(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
-            umma_pair_bf16(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+            // both descriptors advance by 16 bf16 (32 e4m3) = 32 bytes inside the swizzled row
+            if (fp8) {
+              umma_pair_e4m3(d_tmem, adesc, bdesc, idesc, (kb | sl) != 0 ? 1u : 0u);
+              umma_pair_e4m3(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+              umma_pair_e4m3(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+              umma_pair_e4m3(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+            } else {
+              umma_pair_bf16(d_tmem, adesc, bdesc, idesc, (kb | sl) != 0 ? 1u : 0u);
+              umma_pair_bf16(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+              umma_pair_bf16(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+              umma_pair_bf16(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+            }
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           umma_pair_commit(smem_u32(&empty_bar[st]));
@@ -318,8 +340,12 @@ umma_pair_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __gri
       noisy = temp > 0.f;
       invT = noisy ? 1.0f / temp : 1.0f;
     }
-    const EpiRow row{b, row_ok, greedy, (p.flags & kFlagExtNoise) != 0, (p.flags & kFlagReturnLogits) != 0,
-                     (p.v_offset & 3) == 0, invT, noisy, resolve_seed(p.seed, p.flags)};
+    EpiRow row{b, row_ok, greedy, (p.flags & kFlagExtNoise) != 0, (p.flags & kFlagReturnLogits) != 0,
+               (p.v_offset & 3) == 0, invT, noisy, resolve_seed(p.seed, p.flags)};
+    if (p.flags & kFlagFp8) {  // e4m3 operands: the accumulator is rescaled per vocabulary row and batch row
+      row.w_scale = p.w_scale;
+      row.h_scale = row_ok ? p.h_scale[b] : 1.f;
+    }
     const int S = p.S;
     const size_t slot_row = ((size_t)cta * kUmmaEpiGroups + wg) * ((size_t)S * p.B);
     float best_val = -INFINITY;

@@ -63,7 +63,7 @@ def test_fp8_logits_match_dequantised_matmul(fs, V, D, B):
 
 
 @pytest.mark.parametrize("V,D,B,S", [(20000, 512, 3, 2), (20000, 512, 48, 1), (30000, 256, 64, 2), (9000, 1024, 130, 1),
-                                     (5000, 128, 300, 1)])
+                                     (5000, 128, 300, 1), (40000, 256, 200, 1), (33000, 512, 256, 2)])
 def test_fp8_external_noise_parity(fs, V, D, B, S):
     w_q, w_s, h = _head(V, D, B, seed=V + B + S)
     g = torch.Generator().manual_seed(S)
