@@ -978,9 +978,14 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
   int parts = launch_umma(*d, c.W_bf16, h_operand, p, stream, 0);
   g_overlap_next = false;
   if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
-  p.topk.nseg = parts / (p.B > 128 ? 2 : 1);  // CTAs x column groups (two column groups per M tile with two M tiles)
-  topk_finish_kernel<<<nb, kTopkFinishThreads, kTopkListCap * sizeof(unsigned long long), stream>>>(p);
-  if (cudaGetLastError() != cudaSuccess) return FMMS_ERR_CUDA;
+  p.topk.nseg = parts;  // CTAs x column groups x segments per thread: 4 x 1 with one M tile, 2 x 2 with two
+  // The follow-up kernels are launched with programmatic stream serialisation: each becomes resident while its
+  // producer still runs and waits (griddepcontrol.wait) for it before touching anything, which hides their launch
+  // latencies behind one another.
+  g_overlap_next = true;
+  if (launch_kernel(topk_finish_kernel, nb, kTopkFinishThreads, kTopkListCap * sizeof(unsigned long long), stream, p) !=
+      cudaSuccess)
+    return FMMS_ERR_CUDA;
   // 3. rows whose list overflowed: a conditional greedy pass writes all logits, then exact selection
   if (exact_pass) {
     SampleParams q = p;
@@ -991,11 +996,16 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
     q.out_val = q.out_logprob = q.out_lse = nullptr;
     q.run_if = p.topk.need_fallback;
     q.topk = TopkArgs{};
+    g_overlap_next = true;
     parts = launch_umma(*d, c.W_bf16, h_operand, q, stream, 0);
+    g_overlap_next = false;
     if (parts <= 0) return parts == 0 ? FMMS_ERR_CUDA : -parts;
-    topk_exact_kernel<<<nb, kTopkExactThreads, 0, stream>>>(p, q.logits_out);
+    g_overlap_next = true;
+    if (launch_kernel(topk_exact_kernel, nb, kTopkExactThreads, 0, stream, p, (const float*)q.logits_out) != cudaSuccess)
+      return FMMS_ERR_CUDA;
   } else {
-    topk_overflow_kernel<<<nb, 128, 0, stream>>>(p);
+    g_overlap_next = true;
+    if (launch_kernel(topk_overflow_kernel, nb, 128, 0, stream, p) != cudaSuccess) return FMMS_ERR_CUDA;
   }
   g_last_path = FMMS_PATH_MMA;
   return cudaGetLastError() == cudaSuccess ? FMMS_OK : FMMS_ERR_CUDA;

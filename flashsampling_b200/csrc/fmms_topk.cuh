@@ -273,6 +273,7 @@ __device__ __forceinline__ void select_kth_key(const unsigned long long* keys, i
 
 // One CTA per batch row.  Dynamic shared memory: kTopkListCap keys.
 __global__ void __launch_bounds__(kTopkFinishThreads) topk_finish_kernel(const SampleParams p) {
+  griddep_wait();  // launched behind its producer with programmatic stream serialisation
   extern __shared__ unsigned long long topk_keys[];
   __shared__ unsigned int hist[2048];
   __shared__ unsigned long long picked[2 * kTopkSlots];
@@ -336,6 +337,7 @@ __global__ void __launch_bounds__(kTopkFinishThreads) topk_finish_kernel(const S
 // Rows that overflowed, from their full logits [B, V] (fp32, unscaled): exact radix selection of the
 // k-th largest scaled logit, then the k largest (equal values: lowest ids first), then the same tail.
 __global__ void __launch_bounds__(kTopkExactThreads) topk_exact_kernel(const SampleParams p, const float* __restrict__ logits) {
+  griddep_wait();  // launched behind its producer with programmatic stream serialisation
   __shared__ unsigned int hist[2048];
   __shared__ unsigned long long picked[2 * kTopkSlots];
   __shared__ unsigned int sh_prefix, sh_need, sh_count, sh_scan[kTopkExactThreads / 32], sh_taken;
@@ -430,6 +432,7 @@ __global__ void __launch_bounds__(kTopkExactThreads) topk_exact_kernel(const Sam
 
 // Rows that overflowed when there is no scratch for the exact pass: ids -1 and an error status.
 __global__ void topk_overflow_kernel(const SampleParams p) {
+  griddep_wait();  // launched behind its producer with programmatic stream serialisation
   const int b = blockIdx.x, tid = threadIdx.x;
   if (b == 0 && tid == 0) *p.topk.need_fallback = 0u;
   if (!p.topk.row_fallback[b]) return;

@@ -566,7 +566,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
                    const __grid_constant__ CUtensorMap h_map, const SampleParams p, const int nt_cap,
                    const int units_total, const int q_units, const int h_rows, const int SK, const int R_,
                    const int m_rows) {
-  if (p.run_if && *reinterpret_cast<const volatile unsigned int*>(p.run_if) == 0u) return;  // conditional launch
+  if (p.run_if) {  // conditional launch: the flag is the previous kernel's to write
+    griddep_wait();
+    if (*reinterpret_cast<const volatile unsigned int*>(p.run_if) == 0u) return;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
@@ -846,10 +849,14 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
     float lse_m = -INFINITY, lse_l = 0.f;  // kFlagLogprob: this thread's share of the row's log-sum-exp
     bool topk_started = false;             // kFlagTopk: the CTA's first tile has been through the grid-wide step
     // kFlagTopk: this thread's private segment of its row's candidates
-    const int topk_seg_id = cta * kColGroups + col_group;
+    // (with two M tiles a thread scans half of every tile, four times the columns of a thread of the one-M-tile
+    // layout: it owns two segments and fills them on alternate tiles, which keeps a segment's expected load -
+    // a few entries - far from its capacity even for a row whose early pivots come out low)
+    constexpr int kSegsPerThread = (MT == 2) ? 2 : 1;
+    const int topk_seg_id = (cta * kColGroups + col_group) * kSegsPerThread;
     unsigned long long* topk_seg =
         TOPK && row_ok ? p.topk.list + ((size_t)b * kTopkMaxSegs + topk_seg_id) * kTopkSegCap : nullptr;
-    int topk_seg_n = 0;
+    int topk_seg_n = 0, topk_seg_n2 = 0;
     // the rows' pivots live in the slack behind the last pipeline stage (the MMA reads that area as operand rows
     // that belong to no batch row; nothing else uses it)
     float* topk_pivots = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes);
@@ -917,7 +924,12 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
         if (!mbar_wait(&epi_bar[2], pivot_phase, abort_flag, p.status_dev)) break;
         pivot_phase ^= 1u;
         const float pivot = row_ok ? topk_pivots[b] : INFINITY;
-        if (warp_ok) topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, topk_seg, topk_seg_n, tmax);
+        if (warp_ok) {
+          if (kSegsPerThread == 2 && (t & 1))
+            topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, topk_seg + kTopkSegCap, topk_seg_n2, tmax);
+          else
+            topk_scan_columns<32>(p, row, t_addr, c_begin, c_end, v0, pivot, true, topk_seg, topk_seg_n, tmax);
+        }
         // later tiles publish their maximum after the scan (the first tile's went out before the grid-wide wait)
         if (!first_tile && row_ok && tmax > -INFINITY)
           atomicMax(&p.topk.table[(size_t)b * kTopkSlots + slot], float_key(tmax));
@@ -960,7 +972,10 @@ umma_sample_kernel(const __grid_constant__ CUtensorMap w_map_q, const __grid_con
       const float m2 = __shfl_down_sync(0xffffffffu, lse_m, 16), l2 = __shfl_down_sync(0xffffffffu, lse_l, 16);
       if (lane < 16) lse_merge(lse_m, lse_l, m2, l2);
     }
-    if (TOPK && row_ok) p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id] = (unsigned int)topk_seg_n;
+    if (TOPK && row_ok) {
+      p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id] = (unsigned int)topk_seg_n;
+      if (kSegsPerThread == 2) p.topk.seg_count[(size_t)b * kTopkMaxSegs + topk_seg_id + 1] = (unsigned int)topk_seg_n2;
+    }
     // merge this thread's winners into the per-(row, draw) keys
     if (!TOPK && S == 1 && R == 1) {
       // One key per row and CTA: the winners of a row's column groups (and half-warps) meet in shared memory,

@@ -204,6 +204,42 @@ def test_overflowing_rows_take_the_exact_pass(fs):
         assert int(status.item()) == 0 and torch.equal(out, samples)
 
 
+@pytest.mark.parametrize("seed,B", [(2, 256), (3, 200)])
+def test_gaussian_rows_stay_out_of_the_exact_pass_with_two_m_tiles(fs, seed, B):
+    """Full-size Gaussian heads at more than 128 rows: a thread of the two-M-tile layout scans four times the
+    columns of the one-M-tile layout, and with a single 16-entry segment per thread one or two rows per call
+    used to overflow (seeds below) and send the whole call through the exact pass (~1 ms instead of ~0.35).
+    Run with a scratch too small for the exact pass, an overflow would be reported in the status word."""
+    from flashsampling_b200 import _lib
+
+    lib = _lib.load()
+    V, D, S, k = 151936, 4096, 1, 50
+    torch.manual_seed(seed)
+    w = (torch.randn(V, D, device=_dev()) * 0.02).bfloat16()
+    h = torch.randn(B, D, device=_dev()).bfloat16()
+    t = torch.tensor(0.7, device=_dev())
+    _, small = _lib.query_topk_workspace(V, B)
+    tws = torch.zeros(small, dtype=torch.uint8, device=_dev())
+    ws = torch.zeros(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out = torch.zeros((B, S), dtype=torch.int64, device=_dev())
+    c = _lib.FmmsCall()
+    c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
+    c.W_bf16, c.H_bf16, c.temperature = w.data_ptr(), h.data_ptr(), t.data_ptr()
+    c.V_local, c.D, c.B, c.S, c.seed = V, D, B, S, 3
+    c.out_idx, c.workspace, c.workspace_bytes = out.data_ptr(), ws.data_ptr(), ws.numel()
+    c.status_dev, c.stream = status.data_ptr(), torch.cuda.current_stream().cuda_stream
+    c.top_k, c.top_p, c.topk_workspace, c.topk_workspace_bytes = k, 0.9, tws.data_ptr(), tws.numel()
+    assert lib.fmms_run(ctypes.byref(c)) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(out.min()) >= 0
+    # and the ids are those of the allowed set
+    logits = (h[:4].float() @ w.float().T).cpu()
+    for r in range(4):
+        allowed = set(_allowed(logits[r], 0.7, k, 0.9)[0].tolist())
+        assert int(out[r, 0]) in allowed
+
+
 def test_top_k_argument_errors(fs):
     w = torch.zeros(256, 16, dtype=torch.bfloat16, device=_dev())
     h = torch.zeros(2, 16, dtype=torch.bfloat16, device=_dev())
