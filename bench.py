@@ -162,6 +162,9 @@ def make_inputs(wl, B, rank, world, device):
     return w, h, t
 
 
+SETTLE_S = 0.4  # idle time in front of every measurement (see time_steps)
+
+
 def time_steps(fn, steps, warmup, flush, dist_barrier):
     """Per-step device times (ms), plus the wall time of the whole timed region.
 
@@ -169,6 +172,11 @@ def time_steps(fn, steps, warmup, flush, dist_barrier):
     256 MB buffer (evicts L2, leaves no dirty lines, and keeps the GPU busy so that the host's
     launch overhead does not show up between the events) or the reference's 256 MB memset.
     """
+    # Every measurement starts from the same clock state: on this pool the SM clock settles ~4 % lower after
+    # ~50 ms of uninterrupted load and comes back after a pause, so a configuration timed right behind another
+    # one's work would inherit the lower clock (and a 5 % longer step).  Applies to every leg, the reference's too.
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_S)
     for _ in range(warmup):
         flush()
         fn()
@@ -420,7 +428,9 @@ def run_b200(args):
     sweep = []
     if args.sweep and world == 1:
         for b in SWEEP_BATCHES:
-            r = measure(b, max(10, args.steps // 2), max(3, args.warmup // 4), with_e2e=False) if b != B else main
+            # the full warm-up: after the pause of building a workload the first ~20 calls run before the clocks
+            # have come back up, which would shift the median of a short run
+            r = measure(b, max(10, args.steps // 2), args.warmup, with_e2e=False) if b != B else main
             us = statistics.median(r["times_ms"]) * 1e3
             gbs = algorithmic_bytes(V, D, b, S) / (us * 1e-6) / 1e9
             sweep.append(dict(B=b, us=round(us, 2), path=r["path"], algo_gbs=round(gbs, 1),
@@ -481,7 +491,8 @@ def run_b200(args):
             "l2": f"cold: a read-only sweep of a 256 MB buffer evicts L2 before every timed call (no dirty lines), and every "
                   f"step streams a different copy of the {v_local * D * 2 / 1e6:.0f} MB weight (shard), {main['n_copies']} "
                   f"copies in rotation",
-            "timing": "CUDA events per call on the launch stream, max over ranks, median over steps",
+            "timing": "CUDA events per call on the launch stream, max over ranks, median over steps; every measurement "
+                             "(this library's and the reference kernel's) starts after a 0.4 s idle pause and its warm-up",
         },
         "p10_us": round(per_call[len(per_call) // 10] * 1e3, 3),
         "p90_us": round(per_call[(len(per_call) * 9) // 10] * 1e3, 3),
@@ -617,7 +628,7 @@ def run_triton_leg(args):
             step()  # compiles and autotunes
             torch.cuda.synchronize()
             n = max(10, args.steps)
-            a, _ = time_steps(step, n, 5, sweep_read, lambda: None)
+            a, _ = time_steps(step, n, max(3, args.warmup), sweep_read, lambda: None)
             b, _ = time_steps(step, n, 5, flush.zero_, lambda: None)
             entry.update(us=round(statistics.median(a) * 1e3, 2), write_flush_us=round(statistics.median(b) * 1e3, 2))
         except Exception as exc:  # a shape the reference's kernel refuses: report, go on
@@ -644,7 +655,7 @@ def reference_triton_sweep(args, batches, steps):
     """Run --triton-leg in a child process (so that a failure of the reference's kernel cannot take the
     benchmark's CUDA context with it) and return {B: entry}, or {"unavailable": reason}."""
     cmd = [sys.executable, str(Path(__file__).resolve()), "--triton-leg", "--workload", args.workload,
-           "--batches", ",".join(map(str, batches)), "--steps", str(steps)]
+           "--batches", ",".join(map(str, batches)), "--steps", str(steps), "--warmup", str(args.warmup)]
     try:
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
         for ln in reversed(res.stdout.strip().splitlines()):
