@@ -86,6 +86,7 @@ __host__ inline UmmaPlan umma_plan(int V, int B, int num_sms, int max_smem, int 
   pl.grid = pl.units_total < num_sms ? pl.units_total : num_sms;
   int u_max = (pl.units_total + pl.grid - 1) / pl.grid;
   pl.h_rows = pl.mt == 2 ? 128 : ((B + 7) / 8 * 8);
+  if (pl.h_rows < 16) pl.h_rows = 16;  // an 8-row hidden-state box measured 2-4 us slower than a 16-row one (half of it zero fill)
   // M = 64 MMAs (at most 64 batch rows, no row replicas; m_force = 0 keeps M = 128) read half the A operand and
   // leave 16 rows in the lower half of every TMEM lane quadrant; the epilogue splits every chunk of columns
   // between the two half-warps, so twice as many lanes scan as with the same rows in an M = 128 accumulator.
