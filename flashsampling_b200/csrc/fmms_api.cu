@@ -877,9 +877,10 @@ int fmms_query_staging(int D, int B, int S, size_t* bytes) {
 // Scratch layout: a head that is zero between calls, laid out for 256 rows whatever the batch (calls of
 // different batch sizes share one scratch, and the parts behind the head keep stale data):
 // [table 256 x 64 u32][segment counts 256 x 640 u32][gbar, need_fallback: 256 B][row_fallback 256][ids of the
-// conditional pass 256 x 8], then [segments B x 640 x 16 x 8][logits B x V x 4].
+// conditional pass 256 x 8][spill counts 256 u32], then [segments B x 640 x 16 x 8][spill lists B x 2048 x 8]
+// [logits B x V x 4].
 struct TopkLayout {
-  size_t table, count, words, rows, dummy_idx, list, logits, total_small, total_full;
+  size_t table, count, words, rows, dummy_idx, extra_count, list, extra, logits, total_small, total_full;
 };
 static TopkLayout topk_layout(int V, int B) {
   TopkLayout l{};
@@ -890,7 +891,9 @@ static TopkLayout topk_layout(int V, int B) {
   l.words = off;     off += 256;
   l.rows = off;      off += align256(rows);
   l.dummy_idx = off; off += align256(rows * 8);
+  l.extra_count = off; off += align256(rows * 4);
   l.list = off;      off += align256((size_t)B * kTopkMaxSegs * kTopkSegCap * 8);
+  l.extra = off;     off += align256((size_t)B * kTopkExtraCap * 8);
   l.total_small = off;
   l.logits = off;    off += align256((size_t)B * V * 4);
   l.total_full = off;
@@ -956,6 +959,8 @@ static int topk_rows(const fmms_call_t& c, int b0, int nb) {
   p.topk.need_fallback = p.topk.gbar + 1;
   p.topk.row_fallback = tw + l.rows;
   p.topk.list = reinterpret_cast<unsigned long long*>(tw + l.list);
+  p.topk.extra_count = reinterpret_cast<unsigned int*>(tw + l.extra_count);
+  p.topk.extra = reinterpret_cast<unsigned long long*>(tw + l.extra);
 
   const void* h_operand = p.H;
   if (c.flags & FMMS_FLAG_W_FP8) {

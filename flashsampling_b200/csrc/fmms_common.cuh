@@ -30,6 +30,8 @@ constexpr int kTopkSlots = 64;       // class maxima per row; also the largest t
 constexpr int kTopkSegCap = 16;      // candidates one epilogue thread can keep for its row (its private segment)
 constexpr int kTopkMaxSegs = 640;    // segments per row: persistent CTAs x column groups
 constexpr int kTopkListCap = 4096;   // candidates per row that the finish kernel gathers from the segments
+constexpr int kTopkSpillDead = 1 << 24;  // a thread's segment count from the moment it found the spill list full
+constexpr int kTopkExtraCap = 2048;  // entries of a row's spill list (logits clustered in a few CTAs' vocabulary ranges)
 struct TopkArgs {
   int k;                        // top_k (1..kTopkSlots); 0 = off
   float top_p;                  // nucleus mass in (0, 1); anything else = off
@@ -38,6 +40,8 @@ struct TopkArgs {
   unsigned int* seg_count;      // [B][kTopkMaxSegs] candidates each thread found (above kTopkSegCap: overflow);
                                 // every launch writes all nseg entries of every row it reads
   unsigned long long* list;     // [B][kTopkMaxSegs][kTopkSegCap] packed (scaled logit, local id)
+  unsigned int* extra_count;    // [B] candidates that did not fit into their thread's segment ...
+  unsigned long long* extra;    // ... and went to the row's shared spill list [B][kTopkExtraCap] instead
   unsigned int* gbar;           // grid-wide arrival counter of the collecting pass
   unsigned int* need_fallback;  // != 0: some row overflowed and the exact pass has to run
   unsigned char* row_fallback;  // [B] rows that overflowed

@@ -291,9 +291,7 @@ __global__ void __launch_bounds__(kTopkFinishThreads) topk_finish_kernel(const S
   const unsigned int* counts = p.topk.seg_count + (size_t)b * kTopkMaxSegs;
   const unsigned long long* segs = p.topk.list + (size_t)b * kTopkMaxSegs * kTopkSegCap;
   for (int sg = tid; sg < p.topk.nseg; sg += kTopkFinishThreads) {
-    const unsigned int c = counts[sg];
-    if (c > (unsigned int)kTopkSegCap) sh_overflow = 1u;
-    const unsigned int n = min(c, (unsigned int)kTopkSegCap);
+    const unsigned int n = min(counts[sg], (unsigned int)kTopkSegCap);  // what did not fit is in the spill list
     if (n) {
       const unsigned int pos = atomicAdd(&sh_total, n);
       for (unsigned int i = 0; i < n; ++i)
@@ -301,9 +299,23 @@ __global__ void __launch_bounds__(kTopkFinishThreads) topk_finish_kernel(const S
     }
   }
   __syncthreads();
+  {
+    // the row's spill list: entries of threads whose segments were full
+    const unsigned int ex = p.topk.extra_count[b], base = sh_total;
+    const unsigned long long* extra = p.topk.extra + (size_t)b * kTopkExtraCap;
+    for (unsigned int i = tid; i < min(ex, (unsigned int)kTopkExtraCap); i += kTopkFinishThreads)
+      if (base + i < (unsigned int)kTopkListCap) topk_keys[base + i] = extra[i];
+    __syncthreads();
+    if (tid == 0) {
+      if (ex > (unsigned int)kTopkExtraCap) sh_overflow = 1u;
+      sh_total = base + ex;
+      p.topk.extra_count[b] = 0u;  // as the next call expects it
+    }
+    __syncthreads();
+  }
   if (sh_overflow || sh_total > (unsigned int)kTopkListCap) {
-    // the running bound did not keep up with this row (or one thread's share of it holds more large logits
-    // than its segment): leave it to the exact pass
+    // the running bound did not keep up with this row (more candidates than the lists hold): leave it to the
+    // exact pass
     if (tid == 0) {
       p.topk.row_fallback[b] = 1;
       atomicExch(p.topk.need_fallback, 1u);

@@ -521,8 +521,15 @@ __device__ __forceinline__ void topk_scan_columns(const SampleParams& p, const E
           const float z = __uint_as_float(acc[i]) * e.inv_t;
           tmax = fmaxf(tmax, z);
           if (append && z >= pivot) {
-            if (seg_n < kTopkSegCap) seg[seg_n] = cand_key(z, vbase + i);
-            ++seg_n;  // beyond the capacity it only counts: the finish kernel sends the row to the exact pass
+            if (seg_n < kTopkSegCap) {
+              seg[seg_n] = cand_key(z, vbase + i);
+            } else if (seg_n < kTopkSpillDead) {
+              // a full segment (large logits clustered in this CTA's vocabulary range): the row's shared spill list
+              const unsigned int pos = atomicAdd(&p.topk.extra_count[e.b], 1u);
+              if (pos < (unsigned int)kTopkExtraCap) p.topk.extra[(size_t)e.b * kTopkExtraCap + pos] = cand_key(z, vbase + i);
+              else seg_n = kTopkSpillDead;  // that list is full too (the count says so): the row goes to the exact pass
+            }
+            ++seg_n;
           }
         }
       }

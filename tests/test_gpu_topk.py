@@ -240,6 +240,46 @@ def test_gaussian_rows_stay_out_of_the_exact_pass_with_two_m_tiles(fs, seed, B):
         assert int(out[r, 0]) in allowed
 
 
+def test_clustered_large_logits_use_the_spill_list(fs):
+    """A head whose first 2000 vocabulary rows carry three times the weight scale (frequent tokens at the low ids
+    of a vocabulary): a couple of hundred of their logits pass the pivot, all inside two CTAs' vocabulary
+    ranges, i.e. eight threads' segments per row.  What does not fit goes to the row's spill list, not to the
+    exact pass: with a scratch too small for that pass no row may be reported, and every id is an allowed one."""
+    from flashsampling_b200 import _lib
+
+    lib = _lib.load()
+    V, D, B, S, k = 151936, 1024, 40, 2, 50
+    torch.manual_seed(11)
+    w = torch.randn(V, D, device=_dev()) * 0.03
+    w[:2000] *= 3.0
+    w = w.bfloat16()
+    h = torch.randn(B, D, device=_dev()).bfloat16()
+    t = torch.tensor(0.8, device=_dev())
+    _, small = _lib.query_topk_workspace(V, B)
+    tws = torch.zeros(small, dtype=torch.uint8, device=_dev())
+    ws = torch.zeros(_lib.query_workspace(V, D, B, S), dtype=torch.uint8, device=_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out = torch.zeros((B, S), dtype=torch.int64, device=_dev())
+    c = _lib.FmmsCall()
+    c.struct_bytes = ctypes.sizeof(_lib.FmmsCall)
+    c.W_bf16, c.H_bf16, c.temperature = w.data_ptr(), h.data_ptr(), t.data_ptr()
+    c.V_local, c.D, c.B, c.S, c.seed = V, D, B, S, 5
+    c.out_idx, c.workspace, c.workspace_bytes = out.data_ptr(), ws.data_ptr(), ws.numel()
+    c.status_dev, c.stream = status.data_ptr(), torch.cuda.current_stream().cuda_stream
+    c.top_k, c.top_p, c.topk_workspace, c.topk_workspace_bytes = k, 0.0, tws.data_ptr(), tws.numel()
+    for _ in range(2):  # the second call finds the spill counters reset
+        assert lib.fmms_run(ctypes.byref(c)) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0 and int(out.min()) >= 0
+        logits = (h.float() @ w.float().T).cpu()
+        inside_cluster = 0
+        for r in range(B):
+            allowed = set(_allowed(logits[r], 0.8, k, None)[0].tolist())
+            assert all(int(x) in allowed for x in out[r].tolist()), r
+            inside_cluster += sum(1 for x in allowed if x < 2000)
+        assert inside_cluster > 0.9 * B * k  # the allowed sets do sit in the clustered range
+
+
 def test_top_k_argument_errors(fs):
     w = torch.zeros(256, 16, dtype=torch.bfloat16, device=_dev())
     h = torch.zeros(2, 16, dtype=torch.bfloat16, device=_dev())
