@@ -570,7 +570,8 @@ int fmms_num_sms(int* num_sms) {
 int fmms_query_workspace(int V_local, int D, int B, int S, size_t* bytes) {
   if (!bytes || V_local <= 0 || D <= 0 || B <= 0 || S <= 0) return FMMS_ERR_BAD_ARG;
   // With several draws per row the tensor-core kernel keeps running candidates in the workspace, one
-  // row per TMEM lane (128) when it replicates a batch of at most 64 rows over the lane quadrants.
+  // row per TMEM lane (128) for a batch of at most 64 rows: with 64-row accumulators two lanes scan for
+  // each row and keep separate candidates.
   const int rows = B > 256 ? 256 : ((S > 1 && B <= 64) ? 128 : B);
   *bytes = workspace_bytes_for(rows, S);
   return FMMS_OK;

@@ -54,7 +54,7 @@ struct SampleParams {
   unsigned int* sched;       // dynamic work counter, zero on entry and on exit
   float* cand_val;           // [4 * gridDim.x, S * cand_rows] running per-CTA candidates (tensor-core path, S > 1)
   int* cand_idx;
-  int cand_rows;             // rows of that scratch: B, or 128 (TMEM lanes) when the kernel runs row replicas
+  int cand_rows;             // rows of that scratch: B, or 128 (one per TMEM lane) with 64-row accumulators or row replicas
   long long* out_idx;        // [B, S]
   float* out_val;            // [B, S] or null
   // kFlagLogprob: per-CTA partial log-sum-exps, the rows' normalisers, and the outputs
