@@ -86,6 +86,20 @@ def test_plan_dispatch_rules(lib):
         _lib.plan(1000, 12, 1, 1)  # D not a multiple of 8 (16-byte rows)
 
 
+def test_plan_details_of_the_tensor_core_kernel(lib):
+    from flashsampling_b200 import _lib
+
+    mma = _lib.FLAG_FORCE_MMA
+    # hidden-state boxes are at least 16 rows high: up to 16 rows plan alike
+    assert _lib.plan(151936, 4096, 3, 1, flags=mma) == _lib.plan(151936, 4096, 16, 1, flags=mma)
+    # 65..128 rows: 8 KiB of slack behind the ring leave room for a fifth stage on the Qwen head
+    p128 = _lib.plan(151936, 4096, 128, 1)
+    assert p128["stages"] == 5 and p128["smem_bytes"] <= 232448
+    # more than 128 rows on a full-size vocabulary: CTA pairs (an even grid), on a short shard two M tiles
+    assert _lib.plan(151936, 4096, 256, 1)["grid"] % 2 == 0 and _lib.plan(151936, 4096, 256, 1)["m_tiles"] == 2
+    assert _lib.plan(18992, 4096, 256, 1)["m_tiles"] == 2
+
+
 def test_python_entry_point_rejects_cpu_tensors_and_bad_shapes():
     import flashsampling_b200 as fs
 
